@@ -1,0 +1,234 @@
+/*
+ * split12_b200 -- C ABI of the B200 (sm_100a) split12 decode + GEMV/GEMM library.
+ *
+ * The first block re-exports, name for name and argument for argument, the
+ * kernel entry points the Turbo-Lossless engine binds (its declarations are at
+ * engine/inference.cpp:22-39 of the reference).  Each declaration cites the
+ * reference definition it replaces.  The second block is the fused superset
+ * the legacy names are implemented on.  The third block is host-side helpers
+ * (no device work) for the load-time steps either side of the path.
+ *
+ * Conventions shared by every device entry point (same as the reference's):
+ *   - all data pointers are DEVICE pointers unless the name says host;
+ *   - bf16 values travel as raw 16-bit patterns;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued
+ *     asynchronously and the call never synchronises (one exception, noted);
+ *   - return 0 on success.  Unlike the reference (which returns 0
+ *     unconditionally) a negative S12_ERR_* is returned, and nothing is
+ *     launched, when the arguments are unusable.
+ *
+ * Packed tensor layout (unchanged on-disk format, split12_pack.c:47-128):
+ *   sm  uint8 [M*K]    sign<<7 | mantissa, row major
+ *   gr  uint8 [M*K/2]  group nibbles, low nibble = even linear index
+ *   exponent = base_exp + group for group 1..15; group 0 marks an escape whose
+ *   exact bf16 is in the CSR list (row_off int32 [M+1], cols int32 [np],
+ *   correct int16 [np], wrong int16 [np]).
+ */
+#ifndef SPLIT12_B200_H
+#define SPLIT12_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define S12_OK               0
+#define S12_ERR_BAD_ARG     -1   /* null pointer, negative or odd size, stride < K ...   */
+#define S12_ERR_UNSUPPORTED -2   /* shape outside what the kernel family handles       */
+#define S12_ERR_CUDA        -3   /* a CUDA runtime/driver call failed (see s12_last_error) */
+#define S12_ERR_TIMEOUT     -4   /* a bounded device-side wait gave up (s12_device_status) */
+#define S12_ERR_TOO_LARGE   -5   /* request exceeds a fixed capacity                     */
+
+/* =========================================================================
+ * 1. Drop-in entry points (reference names and signatures)
+ * ========================================================================= */
+
+/* B=1 GEMV, out[m] = sum_k dec(W[m,k]) * act[k], escapes decoded with
+ * exponent base_exp ("wrong"), fp32 out.  Replaces nvidia_kernels.cu:385-400. */
+int nv_launch_split12_v2_async(const void* sm, const void* gr, int base_exp,
+                               const void* act, void* out, int M, int K, void* stream);
+
+/* Two tensors (gate, up) sharing one activation vector.
+ * Replaces nvidia_kernels.cu:402-412. */
+int nv_launch_split12_v2_dual_async(const void* sm_a, const void* gr_a, int base_exp_a,
+                                    const void* sm_b, const void* gr_b, int base_exp_b,
+                                    const void* act, void* out_a, void* out_b,
+                                    int M, int K, void* stream);
+
+/* out[row] += sum_p (correct_p - wrong_p) * act[col_p] over the CSR list.
+ * Replaces nvidia_kernels.cu:414-424. */
+int nv_launch_patches_async(const void* row_off, const void* cols, const void* correct,
+                            const void* wrong, const void* act, void* out, int M, void* stream);
+
+/* Same for B sequences, only over the listed non-empty rows;
+ * out[b*out_stride + row].  Replaces nvidia_kernels.cu:426-442. */
+int nv_launch_patches_batch_async(const void* row_off, const void* cols, const void* correct,
+                                  const void* wrong, const void* nonempty_rows, int num_nonempty,
+                                  const void* act, int act_stride, void* out, int out_stride,
+                                  int B, void* stream);
+
+/* Fused decode + GEMM: out[b*out_stride + m] = sum_k dec(W[m,k]) * act[b*act_stride + k].
+ * With the four patch pointers null (what the engine passes) escapes stay
+ * "wrong"; with all four given the escapes are exact.  Unlike the reference's
+ * kernels act_stride is honoured.  Replaces nvidia_kernels.cu:444-524. */
+int nv_launch_split12_fused_gemm_async(const void* sm, const void* gr, int base_exp,
+                                       const void* act, int act_stride,
+                                       void* out, int out_stride,
+                                       int M, int K, int B, void* stream,
+                                       const void* patch_row_off, const void* patch_cols,
+                                       const void* patch_correct, const void* patch_wrong);
+
+/* Same 15 arguments; the reference's separate "V3" export.
+ * Replaces nvidia_kernels_v3.cu:16-83. */
+int nv_launch_split12_fused_gemm_v3_async(const void* sm, const void* gr, int base_exp,
+                                          const void* act, int act_stride,
+                                          void* out, int out_stride,
+                                          int M, int K, int B, void* stream,
+                                          const void* patch_row_off, const void* patch_cols,
+                                          const void* patch_correct, const void* patch_wrong);
+
+/* The reference decodes into bf16_weight_buf on a private stream and calls a
+ * library GEMM.  Here the same result (escapes "wrong") comes from the fused
+ * kernel; bf16_weight_buf / buf_half_elems are accepted and left untouched.
+ * Replaces nvidia_kernels.cu:550-584. */
+int nv_launch_split12_cublas_batch_async(const void* sm, const void* gr, int base_exp,
+                                         const void* act, int act_stride,
+                                         void* out, int out_stride,
+                                         void* bf16_weight_buf, int buf_half_elems,
+                                         int M, int K, int B, void* stream);
+
+/* Portable twins of the two GEMV entry points.  Replace decompress_v2.hip:530-564. */
+int launch_split12_v2_async(const void* sm, const void* gr, int base_exp,
+                            const void* act, void* out, int M, int K, void* stream);
+int launch_split12_v2_dual_async(const void* sm_a, const void* gr_a, int base_exp_a,
+                                 const void* sm_b, const void* gr_b, int base_exp_b,
+                                 const void* act, void* out_a, void* out_b,
+                                 int M, int K, void* stream);
+
+/* Patch correction on the default stream followed by a device synchronise
+ * (the one synchronising entry point), and its async form.
+ * Replace decompress_v2.hip:102-122. */
+int launch_patches_v2(const void* row_off, const void* cols, const void* correct,
+                      const void* wrong, const void* act, void* out, int M);
+int launch_patches_v2_async(const void* row_off, const void* cols, const void* correct,
+                            const void* wrong, const void* act, void* out, int M, void* stream);
+
+/* Up to 8 tensors corrected by one launch.  descs_cpu points at HOST
+ * descriptors laid out as the reference's PatchBatchDesc (56 bytes each, below);
+ * they are passed to the kernel by value, so descs_gpu is not written and no
+ * host-to-device copy is enqueued.  Replaces decompress_v2.hip:129-139. */
+typedef struct S12PatchBatchDesc {
+    const int32_t* row_offsets;
+    const int32_t* patch_cols;
+    const int16_t* patch_correct;
+    const int16_t* patch_wrong;
+    const int16_t* activations;
+    float*         output;
+    int            M;
+} S12PatchBatchDesc;
+int launch_patches_b1_batched_async(void* descs_gpu, const void* descs_cpu,
+                                    int num_descs, int max_M, void* stream);
+
+/* B=4 / B=8 GEMV with exact escapes read from the thread-stride escape table
+ * (esc_vals ordered by (row, col mod 256, col); esc_row_base[M];
+ * esc_counts[M*256] optional).  All three null means "no escapes".
+ * Replace decompress_v2.hip:860-899. */
+int launch_split12_batch4_async(const void* sm, const void* gr, int base_exp,
+                                const void* a0, const void* a1, const void* a2, const void* a3,
+                                const void* esc_row_base, const void* esc_counts, const void* esc_vals,
+                                void* o0, void* o1, void* o2, void* o3,
+                                int M, int K, void* stream);
+int launch_split12_batch8_async(const void* sm, const void* gr, int base_exp,
+                                const void* a0, const void* a1, const void* a2, const void* a3,
+                                const void* a4, const void* a5, const void* a6, const void* a7,
+                                const void* esc_row_base, const void* esc_counts, const void* esc_vals,
+                                void* o0, void* o1, void* o2, void* o3,
+                                void* o4, void* o5, void* o6, void* o7,
+                                int M, int K, void* stream);
+
+/* =========================================================================
+ * 2. Fused superset
+ * ========================================================================= */
+
+/* One packed tensor as the kernels see it (mirrors the device-pointer part of
+ * CompressedWeight, engine/model.h:21-40).  CSR pointers may all be null. */
+typedef struct S12Tensor {
+    const uint8_t* sm;
+    const uint8_t* gr;
+    const int32_t* row_off;
+    const int32_t* cols;
+    const int16_t* correct;
+    const int16_t* wrong;
+    int M;
+    int K;
+    int base_exp;
+    int num_patches;
+} S12Tensor;
+
+/* Standalone lossless decompress: out_bf16[M*K] = exact bf16 bits (escapes
+ * patched from the CSR list inside the same kernel).  With null CSR pointers
+ * the result equals nv_decode_split12_to_bf16 (nvidia_kernels.cu:533-548). */
+int s12_decompress_async(const S12Tensor* w, void* out_bf16, void* stream);
+
+/* B=1 GEMV over up to S12_MAX_MULTI tensors that share K and the activation
+ * vector (q/k/v, gate/up) in ONE launch, escapes corrected in the same
+ * kernel when a tensor carries its CSR list.  outs[i] is fp32 [w[i].M]. */
+#define S12_MAX_MULTI 4
+int s12_gemv_async(const S12Tensor* w, int num_tensors, const void* act,
+                   void* const* outs, void* stream);
+
+/* Small-batch GEMV, 1 <= B <= 16: out[b*out_stride + m], act[b*act_stride + k]. */
+int s12_gemv_batched_async(const S12Tensor* w, const void* act, int act_stride,
+                           void* out, int out_stride, int B, void* stream);
+
+/* Batched decode + GEMM on the tensor cores, any B >= 1 (dispatches to the
+ * GEMV family for small B).  Exact escapes when w carries its CSR list. */
+int s12_gemm_async(const S12Tensor* w, const void* act, int act_stride,
+                   void* out, int out_stride, int B, void* stream);
+
+/* Programmatic dependent launch for every kernel of this library on the
+ * calling thread's subsequent calls: a kernel may start while its predecessor
+ * in the stream drains and prefetch its (read-only) weights before waiting
+ * for the predecessor's results.  Off by default.  Returns the old setting. */
+int s12_set_dependent_launch(int enable);
+
+/* Text of the last error on this thread ("" if none). */
+const char* s12_last_error(void);
+/* Library version: major*10000 + minor*100 + patch. */
+int s12_version(void);
+/* Reads and clears the device-side status word of the current device
+ * (0 = ok; non-zero = a bounded wait expired; bits name the site).
+ * Synchronises the device. */
+int s12_device_status(void);
+
+/* =========================================================================
+ * 3. Host-side helpers (pure CPU; pointers are HOST pointers)
+ * ========================================================================= */
+
+/* Escape table of the batch4/8 path from the CSR list, and the non-empty row
+ * list of the batched patch kernel.  counts may be null.  Returns the number
+ * of non-empty rows.  Replaces engine/model.cpp:86-156. */
+int s12_host_build_escape_table(const int32_t* row_off, const int32_t* cols,
+                                const int16_t* correct, int M,
+                                int32_t* row_base, uint8_t* counts, int16_t* vals,
+                                int32_t* nonempty_rows);
+
+/* Tensor-parallel shards of a packed tensor (new: the reference is single
+ * GPU).  Outputs are caller-allocated for the worst case (all escapes of the
+ * source).  Return the shard's escape count, or a negative S12_ERR_*.
+ *   rows [r0,r1): column-parallel projection (wq wk wv gate up lm_head)
+ *   cols [c0,c1): row-parallel projection (wo down), c0 and c1 even; the
+ *                 shard is re-laid out dense [M][c1-c0].                    */
+int64_t s12_host_shard_rows(const S12Tensor* src, int r0, int r1,
+                            uint8_t* sm, uint8_t* gr, int32_t* row_off,
+                            int32_t* cols, int16_t* correct, int16_t* wrong);
+int64_t s12_host_shard_cols(const S12Tensor* src, int c0, int c1,
+                            uint8_t* sm, uint8_t* gr, int32_t* row_off,
+                            int32_t* cols, int16_t* correct, int16_t* wrong);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPLIT12_B200_H */

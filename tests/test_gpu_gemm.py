@@ -1,0 +1,83 @@
+"""Batched decode + GEMM entry points vs the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close, dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    from turbo_lossless_b200 import Split12Engine
+    return Split12Engine()
+
+
+def _cw(p, **kw):
+    from turbo_lossless_b200 import CompressedWeight
+    return CompressedWeight.from_packed(p, **kw)
+
+
+def _case(O, M, K, B, seed, frac=1e-3):
+    w = O.synth_weights(M, K, seed, outlier_frac=frac)
+    return w, O.pack(w), O.synth_acts(B, K, seed)
+
+
+@pytest.mark.parametrize("B", [1, 2, 16, 17, 48, 64, 128, 256])
+@pytest.mark.parametrize("M,K", [(128, 256), (200, 512), (4096, 4096), (1024, 4096)])
+def test_legacy_gemm_two_pass(eng, O, M, K, B):
+    """nv_launch_split12_fused_gemm_async with null patch pointers (what the engine passes), then
+    nv_launch_patches_batch_async on the non-empty rows: the reference's batched two passes."""
+    if M * K * B > 4096 * 4096 * 64 and B not in (64, 256):
+        pytest.skip("oracle time")
+    w, p, x = _case(O, M, K, B, B + M)
+    cw, xd = _cw(p), dev(x)
+    out = torch.full((B, M), float("nan"), device="cuda")
+    eng.gemm_only(cw, xd, out, K, M, B)
+    assert_close(out, O.gemm_twopass(p, x, patches=False), what="first pass")
+    eng.patches_batch(cw, xd, out, K, M, B)
+    assert_close(out, O.gemm_twopass(p, x), what="two pass")
+
+
+@pytest.mark.parametrize("B", [16, 48, 64, 256])
+def test_v3_and_cublas_entry_points(eng, O, B):
+    M, K = 256, 1024
+    w, p, x = _case(O, M, K, B, 7)
+    cw, xd = _cw(p), dev(x)
+    ref = O.gemm_twopass(p, x, patches=False)
+    out = torch.empty((B, M), device="cuda")
+    eng.gemm_only(cw, xd, out, K, M, B, v3=True)
+    assert_close(out, ref, what="v3")
+    out.fill_(float("nan"))
+    eng.gemm_cublas_path(cw, xd, out, K, M, B)
+    assert_close(out, ref, what="cublas-path entry point")
+
+
+@pytest.mark.parametrize("B", [24, 64, 100, 256])
+@pytest.mark.parametrize("M,K", [(128, 256), (130, 320), (4096, 4096)])
+def test_fused_exact_with_strides(eng, O, M, K, B):
+    w, p, x = _case(O, M, K, B, 3 * B + M, frac=2e-3)
+    act_stride, out_stride = K + 64, M + 8
+    xd = torch.zeros((B, act_stride), dtype=torch.int16, device="cuda")
+    xd[:, :K] = dev(x)
+    out = torch.full((B, out_stride), float("nan"), device="cuda")
+    eng.gemm(_cw(p), xd, out, act_stride, out_stride, B)
+    assert_close(out[:, :M], O.gemm_exact(w, x), what="fused gemm")
+    assert torch.isnan(out[:, M:]).all()
+    # the legacy name with all four patch pointers given is exact too
+    out2 = torch.empty((B, out_stride), device="cuda")
+    eng.gemm_only(_cw(p), xd, out2, act_stride, out_stride, B, patched=True)
+    assert_close(out2[:, :M], O.gemm_exact(w, x), what="legacy gemm with patch pointers")
+
+
+def test_zero_batch_and_bad_strides(eng, O):
+    w, p, x = _case(O, 128, 256, 4, 1)
+    cw, xd = _cw(p), dev(x)
+    out = torch.empty((4, 128), device="cuda")
+    lib = eng.lib
+    args = (cw.split_sm.data_ptr(), cw.split_gr.data_ptr(), p.base_exp, xd.data_ptr())
+    assert lib.nv_launch_split12_fused_gemm_async(*args, 256, out.data_ptr(), 128, 128, 256, 0, None,
+                                                  None, None, None, None) == 0
+    assert lib.nv_launch_split12_fused_gemm_async(*args, 100, out.data_ptr(), 128, 128, 256, 4, None,
+                                                  None, None, None, None) < 0

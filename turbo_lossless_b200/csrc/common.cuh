@@ -1,0 +1,156 @@
+// Shared device primitives and host runtime glue of the split12 B200 library.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include "../../include/split12_b200.h"
+
+namespace s12 {
+
+// ---------------------------------------------------------------------------
+// host runtime glue (defined in runtime.cu)
+// ---------------------------------------------------------------------------
+int  fail(int code, const char* fmt, ...);          // records the message, returns code
+int  check_cuda(cudaError_t e, const char* what);   // S12_OK or S12_ERR_CUDA
+bool dependent_launch_enabled();
+int  sm_count();                                    // SMs of the current device (cached)
+unsigned int* device_status_word();                 // per-device status word (device pointer)
+
+// Launches `kernel` on `stream`; when dependent launch is enabled the launch
+// carries the programmatic-stream-serialization attribute so that the kernel
+// may begin before its predecessor in the stream has finished.
+template <typename... KArgs, typename... Args>
+int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
+           const char* name, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    if (dependent_launch_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...), name);
+}
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// Byte permute with sign replication: selector nibble n picks byte (n & 7) of
+// {a (0-3), b (4-7)}; bit 3 of the nibble replaces the byte by 8 copies of its
+// most significant bit.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// Streaming 16-byte / 8-byte loads of read-only weights: no L1 allocation.
+__device__ __forceinline__ uint4 ldg_stream16(const void* p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream8(const void* p)
+{
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+                 : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// Programmatic dependent launch: wait for the predecessor grid's results /
+// allow the successor grid to start.  Both are no-ops when the kernel was
+// launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t h) { return __uint_as_float(h << 16); }
+
+// mma.sync m16n8k16, bf16 inputs, fp32 accumulate (in place).
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1,
+                                               uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------------------
+// split12 decode, eight weights at a time
+// ---------------------------------------------------------------------------
+// Element semantics (nvidia_kernels.cu:540-547 of the reference):
+//     bf16 = sign<<15 | (base_exp + group)<<7 | mantissa      (16-bit truncation)
+// with sm = sign<<7 | mantissa and group the nibble of gr.
+//
+// Inputs: s_lo = sm bytes of elements 0..3, s_hi = elements 4..7 (little
+// endian), g = the four gr bytes = eight nibbles, element i in bits 4i..4i+3.
+// Output: four bf16x2 registers pairing element i (low half) with element i+4
+// (high half):  p[0]=(e0,e4)  p[1]=(e1,e5)  p[2]=(e2,e6)  p[3]=(e3,e7).
+// That pairing makes both exponent nibbles of a pair sit 16 bits apart in g, so
+// one mask and one shift-add places them; the sign+mantissa halves come from a
+// single sign-replicating byte permute.  About 2.1 integer instructions per
+// weight.  base2 = ((base_exp<<7) & 0xFFFF) * 0x10001.
+//
+// kMode 0: base_exp >= 0, the fast form above.
+// kMode 1: base_exp < 0 (window starting at exponent 0): the per-half sum can
+//          carry out of 16 bits, so the halves are added independently; an
+//          escape decodes to the reference's bits (exponent field 0xFF).
+// kMode 2: as 1, but escapes (group 0) decode to +0 so that a caller can add
+//          the exact escape values instead of (correct - wrong).
+template <int kMode>
+__device__ __forceinline__ void decode8(uint32_t s_lo, uint32_t s_hi, uint32_t g, uint32_t base2,
+                                        uint32_t (&p)[4])
+{
+    const uint32_t g8 = g >> 8;
+    uint32_t e[4], m[4];
+    e[0] = (g  & 0x000F000Fu) << 7;
+    e[1] = (g  & 0x00F000F0u) << 3;
+    e[2] = (g8 & 0x000F000Fu) << 7;
+    e[3] = (g8 & 0x00F000F0u) << 3;
+    m[0] = prmt(s_lo, s_hi, 0xC480u) & 0x807F807Fu;
+    m[1] = prmt(s_lo, s_hi, 0xD591u) & 0x807F807Fu;
+    m[2] = prmt(s_lo, s_hi, 0xE6A2u) & 0x807F807Fu;
+    m[3] = prmt(s_lo, s_hi, 0xF7B3u) & 0x807F807Fu;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (kMode == 0) {
+            p[i] = m[i] | (e[i] + base2);
+        } else {
+            uint32_t lo = ((e[i] & 0xFFFFu) + (base2 & 0xFFFFu)) & 0xFFFFu;
+            uint32_t hi = ((e[i] >> 16) + (base2 >> 16)) << 16;
+            uint32_t v = m[i] | lo | hi;
+            if (kMode == 2)
+                v &= ((e[i] & 0xFFFFu) ? 0xFFFFu : 0u) | ((e[i] >> 16) ? 0xFFFF0000u : 0u);
+            p[i] = v;
+        }
+    }
+}
+
+// Non-zero iff one of the eight nibbles of g is zero (an escape is present).
+__device__ __forceinline__ uint32_t zero_nibbles(uint32_t g)
+{
+    return (g - 0x11111111u) & ~g & 0x88888888u;
+}
+
+__host__ __device__ __forceinline__ uint32_t make_base2(int base_exp)
+{
+    return (((uint32_t)base_exp << 7) & 0xFFFFu) * 0x10001u;
+}
+
+#endif  // __CUDACC__
+}  // namespace s12

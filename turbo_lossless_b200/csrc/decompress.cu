@@ -1,0 +1,140 @@
+// Standalone split12 -> bf16 decompress (lossless when the CSR list is given).
+//
+// HBM-bound: 1.5 bytes read and 2 bytes written per weight.  One thread owns
+// 16 consecutive elements: one 16-byte load of sm, one 8-byte load of gr, two
+// 16-byte streaming stores.  An escape (group nibble 0) is detected with three
+// integer instructions per eight weights; the thread that meets one looks its
+// exact value up in the row's CSR slice (columns ascend, so a binary search)
+// and overwrites the element after its own vector store, so the patch needs no
+// second pass and no ordering between threads.
+//
+// Replaces nv_decode_split12_to_bf16 (nvidia_kernels.cu:533-548 of the
+// reference), which leaves escapes wrong.
+#include "common.cuh"
+
+namespace s12 {
+
+__device__ __forceinline__ void natural_order(const uint32_t (&p)[4], uint32_t (&o)[4])
+{
+    o[0] = prmt(p[0], p[1], 0x5410u);   // e0 e1
+    o[1] = prmt(p[2], p[3], 0x5410u);   // e2 e3
+    o[2] = prmt(p[0], p[1], 0x7632u);   // e4 e5
+    o[3] = prmt(p[2], p[3], 0x7632u);   // e6 e7
+}
+
+__device__ __forceinline__ void patch_escapes8(uint32_t g, int64_t elem0, int row, int col0,
+                                               const int32_t* __restrict__ row_off,
+                                               const int32_t* __restrict__ cols,
+                                               const int16_t* __restrict__ correct,
+                                               uint16_t* __restrict__ out)
+{
+    int lo0 = row_off[row], hi0 = row_off[row + 1];
+#pragma unroll 1
+    for (int i = 0; i < 8; i++) {
+        if (((g >> (4 * i)) & 0xFu) != 0u) continue;
+        int col = col0 + i, lo = lo0, hi = hi0;
+        while (lo < hi) {                       // first p with cols[p] >= col
+            int mid = (lo + hi) >> 1;
+            if (cols[mid] < col) lo = mid + 1; else hi = mid;
+        }
+        if (lo < hi0 && cols[lo] == col) out[elem0 + i] = (uint16_t)correct[lo];
+    }
+}
+
+// Fast path: K % 16 == 0.  kChunks chunks of 16 elements per thread.
+template <int kMode, int kChunks>
+__global__ void __launch_bounds__(256)
+decompress16_kernel(const uint8_t* __restrict__ sm, const uint8_t* __restrict__ gr, uint32_t base2,
+                    const int32_t* __restrict__ row_off, const int32_t* __restrict__ cols,
+                    const int16_t* __restrict__ correct,
+                    uint16_t* __restrict__ out, int64_t num_chunks, int K)
+{
+    uint4 s[kChunks]; uint2 g[kChunks]; int64_t c[kChunks];
+#pragma unroll
+    for (int j = 0; j < kChunks; j++) {
+        c[j] = ((int64_t)blockIdx.x * kChunks + j) * 256 + threadIdx.x;
+        if (c[j] < num_chunks) {
+            s[j] = ldg_stream16(sm + c[j] * 16);
+            g[j] = ldg_stream8(gr + c[j] * 8);
+        }
+    }
+    grid_launch_dependents();
+    grid_dependency_wait();     // the output buffer may still be read by the predecessor
+#pragma unroll
+    for (int j = 0; j < kChunks; j++) {
+        if (c[j] >= num_chunks) continue;
+        uint32_t p[4], o[4];
+        uint4* dst = reinterpret_cast<uint4*>(out + c[j] * 16);
+        decode8<kMode>(s[j].x, s[j].y, g[j].x, base2, p);
+        natural_order(p, o);
+        __stcs(dst, make_uint4(o[0], o[1], o[2], o[3]));
+        decode8<kMode>(s[j].z, s[j].w, g[j].y, base2, p);
+        natural_order(p, o);
+        __stcs(dst + 1, make_uint4(o[0], o[1], o[2], o[3]));
+        if (row_off != nullptr && (zero_nibbles(g[j].x) | zero_nibbles(g[j].y))) {
+            int64_t e0 = c[j] * 16;
+            int row = (int)(e0 / K);
+            int col = (int)(e0 - (int64_t)row * K);
+            patch_escapes8(g[j].x, e0, row, col, row_off, cols, correct, out);
+            patch_escapes8(g[j].y, e0 + 8, row, col + 8, row_off, cols, correct, out);
+        }
+    }
+}
+
+// General path: any even K.  One thread per pair of elements.
+__global__ void __launch_bounds__(256)
+decompress2_kernel(const uint8_t* __restrict__ sm, const uint8_t* __restrict__ gr, int base_exp,
+                   const int32_t* __restrict__ row_off, const int32_t* __restrict__ cols,
+                   const int16_t* __restrict__ correct,
+                   uint16_t* __restrict__ out, int64_t num_pairs, int K)
+{
+    int64_t pr = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (pr >= num_pairs) return;
+    grid_dependency_wait();
+    uint32_t gb = gr[pr];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        int64_t i = pr * 2 + h;
+        uint32_t s = sm[i], grp = h ? (gb >> 4) : (gb & 0xFu);
+        uint32_t bits = ((s >> 7) << 15) | ((uint32_t)(base_exp + (int)grp) << 7) | (s & 0x7Fu);
+        if (grp == 0u && row_off != nullptr) {
+            int row = (int)(i / K), col = (int)(i - (int64_t)row * K);
+            int lo = row_off[row], hi0 = row_off[row + 1], hi = hi0;
+            while (lo < hi) { int mid = (lo + hi) >> 1; if (cols[mid] < col) lo = mid + 1; else hi = mid; }
+            if (lo < hi0 && cols[lo] == col) bits = (uint16_t)correct[lo];
+        }
+        out[i] = (uint16_t)bits;
+    }
+}
+
+}  // namespace s12
+
+extern "C" int s12_decompress_async(const S12Tensor* w, void* out_bf16, void* stream)
+{
+    using namespace s12;
+    if (!w || !out_bf16) return fail(S12_ERR_BAD_ARG, "s12_decompress_async: null argument");
+    if (w->M < 0 || w->K < 0 || (w->K & 1)) return fail(S12_ERR_BAD_ARG, "s12_decompress_async: M=%d K=%d (K must be even)", w->M, w->K);
+    if (w->M == 0 || w->K == 0) return S12_OK;
+    if (!w->sm || !w->gr) return fail(S12_ERR_BAD_ARG, "s12_decompress_async: null sm/gr");
+    const bool csr = w->row_off && w->cols && w->correct;
+    const int32_t* ro = csr ? w->row_off : nullptr;
+    int64_t n = (int64_t)w->M * w->K;
+    if ((w->K % 16) == 0 && (reinterpret_cast<uintptr_t>(w->sm) % 16) == 0 &&
+        (reinterpret_cast<uintptr_t>(w->gr) % 8) == 0 && (reinterpret_cast<uintptr_t>(out_bf16) % 16) == 0) {
+        constexpr int kChunks = 4;
+        int64_t chunks = n / 16;
+        int64_t blocks = (chunks + 256 * kChunks - 1) / (256 * kChunks);
+        if (blocks > 0x7FFFFFFF) return fail(S12_ERR_TOO_LARGE, "s12_decompress_async: tensor too large");
+        uint32_t base2 = make_base2(w->base_exp);
+        if (w->base_exp >= 0)
+            return launch(decompress16_kernel<0, kChunks>, dim3((unsigned)blocks), dim3(256), 0, stream, "decompress16",
+                          w->sm, w->gr, base2, ro, w->cols, w->correct, (uint16_t*)out_bf16, chunks, w->K);
+        return launch(decompress16_kernel<1, kChunks>, dim3((unsigned)blocks), dim3(256), 0, stream, "decompress16",
+                      w->sm, w->gr, base2, ro, w->cols, w->correct, (uint16_t*)out_bf16, chunks, w->K);
+    }
+    int64_t pairs = n / 2;
+    int64_t blocks = (pairs + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return fail(S12_ERR_TOO_LARGE, "s12_decompress_async: tensor too large");
+    return launch(decompress2_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, "decompress2",
+                  w->sm, w->gr, w->base_exp, ro, w->cols, w->correct, (uint16_t*)out_bf16, pairs, w->K);
+}

@@ -1,0 +1,93 @@
+// Batched decode + GEMM entry points and their dispatcher.
+//
+//   B <= 16 : the MMA GEMV family (gemv.cu), HBM-bound.
+//   B  > 16 : the tcgen05 / TMEM kernel (gemm_tc.cu) when the shape qualifies,
+//             else the GEMV family over 16-column slices of the batch.
+#include "common.cuh"
+
+namespace s12 {
+int gemv_strided(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
+                 int B, void* stream, const char* who);
+int gemm_tc_supported(const S12Tensor* w, int act_stride, int out_stride, int B);
+int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
+                   int B, void* stream, const char* who);
+
+int gemm_dispatch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
+                  int B, void* stream, const char* who)
+{
+    if (!w) return fail(S12_ERR_BAD_ARG, "%s: null tensor", who);
+    if (B == 0 || w->M == 0) return S12_OK;
+    if (B < 0 || w->M < 0 || w->K < 0 || (w->K & 1))
+        return fail(S12_ERR_BAD_ARG, "%s: M=%d K=%d B=%d", who, w->M, w->K, B);
+    if (!act || !out) return fail(S12_ERR_BAD_ARG, "%s: null activations/output", who);
+    if (act_stride < w->K || out_stride < w->M)
+        return fail(S12_ERR_BAD_ARG, "%s: act_stride=%d (K=%d) out_stride=%d (M=%d)", who, act_stride, w->K, out_stride, w->M);
+    if (B > 16 && gemm_tc_supported(w, act_stride, out_stride, B))
+        return gemm_tc_launch(w, act, act_stride, out, out_stride, B, stream, who);
+    for (int b0 = 0; b0 < B; b0 += 16) {
+        int nb = B - b0 < 16 ? B - b0 : 16;
+        int rc = gemv_strided(w, (const uint16_t*)act + (size_t)b0 * act_stride, act_stride,
+                              (float*)out + (size_t)b0 * out_stride, out_stride, nb, stream, who);
+        if (rc) return rc;
+    }
+    return S12_OK;
+}
+
+static int legacy_gemm(const void* sm, const void* gr, int base_exp, const void* act, int act_stride,
+                       void* out, int out_stride, int M, int K, int B, void* stream,
+                       const void* p_ro, const void* p_co, const void* p_cv, const void* p_wv,
+                       const char* who)
+{
+    S12Tensor t = {};
+    t.sm = (const uint8_t*)sm; t.gr = (const uint8_t*)gr; t.M = M; t.K = K; t.base_exp = base_exp;
+    if (p_ro && p_co && p_cv && p_wv) {
+        t.row_off = (const int32_t*)p_ro; t.cols = (const int32_t*)p_co;
+        t.correct = (const int16_t*)p_cv; t.wrong = (const int16_t*)p_wv;
+        t.num_patches = -1;     // unknown to this entry point
+    }
+    return gemm_dispatch(&t, act, act_stride, out, out_stride, B, stream, who);
+}
+
+}  // namespace s12
+
+extern "C" {
+
+int s12_gemm_async(const S12Tensor* w, const void* act, int act_stride,
+                   void* out, int out_stride, int B, void* stream)
+{
+    return s12::gemm_dispatch(w, act, act_stride, out, out_stride, B, stream, "s12_gemm_async");
+}
+
+int nv_launch_split12_fused_gemm_async(const void* sm, const void* gr, int base_exp,
+                                       const void* act, int act_stride, void* out, int out_stride,
+                                       int M, int K, int B, void* stream,
+                                       const void* patch_row_off, const void* patch_cols,
+                                       const void* patch_correct, const void* patch_wrong)
+{
+    return s12::legacy_gemm(sm, gr, base_exp, act, act_stride, out, out_stride, M, K, B, stream,
+                            patch_row_off, patch_cols, patch_correct, patch_wrong,
+                            "nv_launch_split12_fused_gemm_async");
+}
+
+int nv_launch_split12_fused_gemm_v3_async(const void* sm, const void* gr, int base_exp,
+                                          const void* act, int act_stride, void* out, int out_stride,
+                                          int M, int K, int B, void* stream,
+                                          const void* patch_row_off, const void* patch_cols,
+                                          const void* patch_correct, const void* patch_wrong)
+{
+    return s12::legacy_gemm(sm, gr, base_exp, act, act_stride, out, out_stride, M, K, B, stream,
+                            patch_row_off, patch_cols, patch_correct, patch_wrong,
+                            "nv_launch_split12_fused_gemm_v3_async");
+}
+
+int nv_launch_split12_cublas_batch_async(const void* sm, const void* gr, int base_exp,
+                                         const void* act, int act_stride, void* out, int out_stride,
+                                         void* bf16_weight_buf, int buf_half_elems,
+                                         int M, int K, int B, void* stream)
+{
+    (void)bf16_weight_buf; (void)buf_half_elems;
+    return s12::legacy_gemm(sm, gr, base_exp, act, act_stride, out, out_stride, M, K, B, stream,
+                            nullptr, nullptr, nullptr, nullptr, "nv_launch_split12_cublas_batch_async");
+}
+
+}  // extern "C"

@@ -1,0 +1,263 @@
+"""Host-side mirror of the Turbo-Lossless engine's interface to the split12 kernels.
+
+``CompressedWeight`` has the fields of the engine's struct of the same name
+(engine/model.h:21-40 of the reference) and is loaded from the same per-tensor
+file family (engine/model.cpp:32-163).  ``Split12Engine`` offers one method per
+call-site macro of engine/inference.cpp (MATVEC_B1_NOPATCH, NV_OR_HIP_PATCHES,
+BATCH4/8_MATVEC, GEMM_ONLY, PATCHES_ASYNC) plus the fused superset calls, each a
+thin wrapper over one C-ABI entry point.  torch is used for device memory and
+streams only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import capi
+from .capi import S12PatchBatchDesc, S12Tensor, check
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(stream=None) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream if isinstance(stream, int) else stream.cuda_stream
+
+
+@dataclass
+class CompressedWeight:
+    """One packed tensor resident on a device (engine/model.h:21-40)."""
+    M: int
+    K: int
+    base_exp: int
+    split_sm: torch.Tensor                     # uint8 [M*K]
+    split_gr: torch.Tensor                     # uint8 [M*K/2]
+    num_patches: int = 0
+    row_offsets: Optional[torch.Tensor] = None     # int32 [M+1]
+    patch_cols: Optional[torch.Tensor] = None      # int32 [np]
+    patch_correct: Optional[torch.Tensor] = None   # int16 [np]
+    patch_wrong: Optional[torch.Tensor] = None     # int16 [np]
+    escape_row_base: Optional[torch.Tensor] = None  # int32 [M]
+    escape_counts: Optional[torch.Tensor] = None    # uint8 [M*256], only when asked for
+    escape_vals: Optional[torch.Tensor] = None      # int16 [np], (row, col%256, col) order
+    patch_nonempty_rows: Optional[torch.Tensor] = None  # int32 [num_nonempty_rows]
+    num_nonempty_rows: int = 0
+    _keep: list = field(default_factory=list, repr=False)
+
+    # -- construction ------------------------------------------------------
+    @classmethod
+    def from_host(cls, M: int, K: int, base_exp: int, sm: np.ndarray, gr: np.ndarray,
+                  row_off: Optional[np.ndarray], cols: Optional[np.ndarray],
+                  correct: Optional[np.ndarray], wrong: Optional[np.ndarray],
+                  device="cuda", escape_table: bool = True, escape_counts: bool = False) -> "CompressedWeight":
+        """Uploads one packed tensor; builds the escape table and non-empty row list on the host
+        (the load-time steps of engine/model.cpp:86-156) with the library's host helper."""
+        dev = torch.device(device)
+        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
+        npat = 0 if cols is None else int(cols.shape[0])
+        w = cls(M=M, K=K, base_exp=int(base_exp), split_sm=up(sm), split_gr=up(gr), num_patches=npat)
+        if npat > 0 and row_off is not None:
+            w.row_offsets, w.patch_cols = up(row_off), up(cols)
+            w.patch_correct, w.patch_wrong = up(correct), up(wrong)
+            if escape_table:
+                lib = capi.load()
+                row_base = np.zeros(M, np.int32)
+                counts = np.zeros(M * 256, np.uint8) if escape_counts else None
+                vals = np.zeros(npat, np.int16)
+                nonempty = np.zeros(M, np.int32)
+                ro = np.ascontiguousarray(row_off, np.int32)
+                co = np.ascontiguousarray(cols, np.int32)
+                cv = np.ascontiguousarray(correct, np.int16)
+                nne = lib.s12_host_build_escape_table(
+                    ro.ctypes.data, co.ctypes.data, cv.ctypes.data, M, row_base.ctypes.data,
+                    None if counts is None else counts.ctypes.data, vals.ctypes.data, nonempty.ctypes.data)
+                if nne < 0:
+                    raise capi.S12Error(f"s12_host_build_escape_table failed with {nne}")
+                w.escape_row_base, w.escape_vals = up(row_base), up(vals)
+                if counts is not None:
+                    w.escape_counts = up(counts)
+                w.num_nonempty_rows = int(nne)
+                if nne > 0:
+                    w.patch_nonempty_rows = up(nonempty[:nne])
+        return w
+
+    @classmethod
+    def from_packed(cls, p, device="cuda", **kw) -> "CompressedWeight":
+        """From any object with fields M, K, base_exp, sm, gr, row_off, cols, correct, wrong."""
+        return cls.from_host(p.M, p.K, p.base_exp, p.sm, p.gr, p.row_off, p.cols, p.correct, p.wrong,
+                             device=device, **kw)
+
+    @classmethod
+    def from_dir(cls, directory: str, prefix: str, device="cuda", **kw) -> "CompressedWeight":
+        """Reads ``<prefix>.dims`` (text ``M K num_patches base_exp``) and the six binary files
+        written by engine/convert_model.py:127-134; missing or empty CSR files mean no escapes."""
+        with open(os.path.join(directory, prefix + ".dims")) as f:
+            parts = f.read().split()
+        if len(parts) < 3:
+            raise ValueError(f"{prefix}.dims: expected 'M K num_patches [base_exp]'")
+        M, K, npat = int(parts[0]), int(parts[1]), int(parts[2])
+        base_exp = int(parts[3]) if len(parts) > 3 else 0
+
+        def rd(suffix, dtype):
+            path = os.path.join(directory, f"{prefix}.{suffix}.bin")
+            if not os.path.exists(path) or os.path.getsize(path) == 0:
+                return None
+            return np.fromfile(path, dtype=dtype)
+
+        sm, gr = rd("sm", np.uint8), rd("gr", np.uint8)
+        if sm is None or gr is None:
+            raise FileNotFoundError(f"split12 files missing for {prefix} (need .sm.bin + .gr.bin)")
+        if sm.size != M * K or gr.size != (M * K + 1) // 2:
+            raise ValueError(f"{prefix}: sm/gr sizes do not match dims {M}x{K}")
+        ro, co = rd("row_off", np.int32), rd("patch_cols", np.int32)
+        cv, wv = rd("patch_correct", np.int16), rd("patch_wrong", np.int16)
+        if npat > 0 and (ro is None or co is None or cv is None or wv is None):
+            raise ValueError(f"{prefix}: {npat} escapes declared but CSR files are missing")
+        if npat > 0 and (ro.size != M + 1 or co.size != npat or cv.size != npat or wv.size != npat):
+            raise ValueError(f"{prefix}: CSR file sizes do not match dims")
+        if npat == 0:
+            ro = co = cv = wv = None
+        return cls.from_host(M, K, base_exp, sm, gr, ro, co, cv, wv, device=device, **kw)
+
+    # -- views -----------------------------------------------------------------
+    def tensor(self, with_csr: bool = True) -> S12Tensor:
+        t = S12Tensor()
+        t.sm, t.gr = self.split_sm.data_ptr(), self.split_gr.data_ptr()
+        t.M, t.K, t.base_exp, t.num_patches = self.M, self.K, self.base_exp, self.num_patches
+        if with_csr and self.num_patches > 0 and self.row_offsets is not None:
+            t.row_off, t.cols = self.row_offsets.data_ptr(), self.patch_cols.data_ptr()
+            t.correct, t.wrong = self.patch_correct.data_ptr(), self.patch_wrong.data_ptr()
+        else:
+            t.num_patches = 0 if not with_csr else self.num_patches
+        return t
+
+    @property
+    def compressed_bytes(self) -> int:
+        return self.M * self.K * 3 // 2
+
+
+class Split12Engine:
+    """Call sites of the engine, one method per macro of engine/inference.cpp."""
+
+    def __init__(self):
+        self.lib = capi.load()
+
+    # ---- B = 1, legacy two-pass (engine/inference.cpp:222-243) ------------------
+    def matvec_b1_nopatch(self, w: CompressedWeight, bf16_in: torch.Tensor, fp32_out: torch.Tensor,
+                          stream=None, portable: bool = False) -> None:
+        fn = self.lib.launch_split12_v2_async if portable else self.lib.nv_launch_split12_v2_async
+        check(fn(_ptr(w.split_sm), _ptr(w.split_gr), w.base_exp, _ptr(bf16_in), _ptr(fp32_out),
+                 w.M, w.K, _stream(stream)), "split12_v2_async")
+
+    def patches(self, w: CompressedWeight, bf16_in: torch.Tensor, fp32_out: torch.Tensor,
+                stream=None, portable: bool = False) -> None:
+        if w.num_patches <= 0 or w.row_offsets is None:
+            return
+        fn = self.lib.launch_patches_v2_async if portable else self.lib.nv_launch_patches_async
+        check(fn(_ptr(w.row_offsets), _ptr(w.patch_cols), _ptr(w.patch_correct), _ptr(w.patch_wrong),
+                 _ptr(bf16_in), _ptr(fp32_out), w.M, _stream(stream)), "patches_async")
+
+    def matvec_dual(self, wa: CompressedWeight, wb: CompressedWeight, bf16_in: torch.Tensor,
+                    out_a: torch.Tensor, out_b: torch.Tensor, stream=None, portable: bool = False) -> None:
+        fn = self.lib.launch_split12_v2_dual_async if portable else self.lib.nv_launch_split12_v2_dual_async
+        check(fn(_ptr(wa.split_sm), _ptr(wa.split_gr), wa.base_exp, _ptr(wb.split_sm), _ptr(wb.split_gr),
+                 wb.base_exp, _ptr(bf16_in), _ptr(out_a), _ptr(out_b), wa.M, wa.K, _stream(stream)),
+              "split12_v2_dual_async")
+
+    def patches_b1_batched(self, items: Sequence[tuple], stream=None) -> None:
+        """items: (weight, bf16_in, fp32_out) triples, at most 8 (fill_patch_desc, inference.cpp:54-66)."""
+        descs = (S12PatchBatchDesc * 8)()
+        n, max_m = 0, 0
+        for w, x, o in items:
+            if w.num_patches <= 0 or w.row_offsets is None:
+                continue
+            d = descs[n]
+            d.row_offsets, d.patch_cols = _ptr(w.row_offsets), _ptr(w.patch_cols)
+            d.patch_correct, d.patch_wrong = _ptr(w.patch_correct), _ptr(w.patch_wrong)
+            d.activations, d.output, d.M = _ptr(x), _ptr(o), w.M
+            max_m = max(max_m, w.M)
+            n += 1
+        check(self.lib.launch_patches_b1_batched_async(None, C.addressof(descs), n, max_m, _stream(stream)),
+              "launch_patches_b1_batched_async")
+
+    # ---- B = 4 / 8 with the escape table (engine/inference.cpp:72-81,369-382) ------
+    def batch_matvec(self, w: CompressedWeight, ins: Sequence[torch.Tensor], outs: Sequence[torch.Tensor],
+                     stream=None) -> None:
+        n = len(ins)
+        if n not in (4, 8) or len(outs) != n:
+            raise ValueError("batch_matvec takes 4 or 8 activation/output vectors")
+        fn = self.lib.launch_split12_batch4_async if n == 4 else self.lib.launch_split12_batch8_async
+        check(fn(_ptr(w.split_sm), _ptr(w.split_gr), w.base_exp, *[_ptr(t) for t in ins],
+                 _ptr(w.escape_row_base), _ptr(w.escape_counts), _ptr(w.escape_vals),
+                 *[_ptr(t) for t in outs], w.M, w.K, _stream(stream)), f"launch_split12_batch{n}_async")
+
+    # ---- batched, legacy two-pass (engine/inference.cpp:540-570) -----------------
+    def gemm_only(self, w: CompressedWeight, bf16_in: torch.Tensor, out: torch.Tensor, n_in: int,
+                  n_out: int, bs: int, stream=None, v3: bool = False, patched: bool = False) -> None:
+        fn = self.lib.nv_launch_split12_fused_gemm_v3_async if v3 else self.lib.nv_launch_split12_fused_gemm_async
+        pp = [None] * 4
+        if patched and w.num_patches > 0:
+            pp = [_ptr(w.row_offsets), _ptr(w.patch_cols), _ptr(w.patch_correct), _ptr(w.patch_wrong)]
+        check(fn(_ptr(w.split_sm), _ptr(w.split_gr), w.base_exp, _ptr(bf16_in), n_in, _ptr(out), n_out,
+                 w.M, w.K, bs, _stream(stream), *pp), "nv_launch_split12_fused_gemm_async")
+
+    def gemm_cublas_path(self, w: CompressedWeight, bf16_in: torch.Tensor, out: torch.Tensor, n_in: int,
+                         n_out: int, bs: int, weight_buf: Optional[torch.Tensor] = None,
+                         weight_buf_half: int = 0, stream=None) -> None:
+        check(self.lib.nv_launch_split12_cublas_batch_async(
+            _ptr(w.split_sm), _ptr(w.split_gr), w.base_exp, _ptr(bf16_in), n_in, _ptr(out), n_out,
+            _ptr(weight_buf), weight_buf_half, w.M, w.K, bs, _stream(stream)),
+            "nv_launch_split12_cublas_batch_async")
+
+    def patches_batch(self, w: CompressedWeight, bf16_in: torch.Tensor, out: torch.Tensor, n_in: int,
+                      n_out: int, bs: int, stream=None) -> None:
+        if w.num_nonempty_rows <= 0:
+            return
+        check(self.lib.nv_launch_patches_batch_async(
+            _ptr(w.row_offsets), _ptr(w.patch_cols), _ptr(w.patch_correct), _ptr(w.patch_wrong),
+            _ptr(w.patch_nonempty_rows), w.num_nonempty_rows, _ptr(bf16_in), n_in, _ptr(out), n_out,
+            bs, _stream(stream)), "nv_launch_patches_batch_async")
+
+    # ---- fused superset --------------------------------------------------------------
+    def gemv(self, ws: Sequence[CompressedWeight], bf16_in: torch.Tensor, outs: Sequence[torch.Tensor],
+             stream=None, exact: bool = True) -> None:
+        """Up to four tensors sharing one activation vector, escapes corrected in the same launch."""
+        n = len(ws)
+        arr = (S12Tensor * n)(*[w.tensor(with_csr=exact) for w in ws])
+        optr = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+        check(self.lib.s12_gemv_async(arr, n, _ptr(bf16_in), optr, _stream(stream)), "s12_gemv_async")
+
+    def gemv_batched(self, w: CompressedWeight, bf16_in: torch.Tensor, out: torch.Tensor, act_stride: int,
+                     out_stride: int, bs: int, stream=None, exact: bool = True) -> None:
+        t = w.tensor(with_csr=exact)
+        check(self.lib.s12_gemv_batched_async(C.byref(t), _ptr(bf16_in), act_stride, _ptr(out), out_stride,
+                                              bs, _stream(stream)), "s12_gemv_batched_async")
+
+    def gemm(self, w: CompressedWeight, bf16_in: torch.Tensor, out: torch.Tensor, act_stride: int,
+             out_stride: int, bs: int, stream=None, exact: bool = True) -> None:
+        t = w.tensor(with_csr=exact)
+        check(self.lib.s12_gemm_async(C.byref(t), _ptr(bf16_in), act_stride, _ptr(out), out_stride, bs,
+                                      _stream(stream)), "s12_gemm_async")
+
+    def decompress(self, w: CompressedWeight, out: Optional[torch.Tensor] = None, stream=None,
+                   exact: bool = True) -> torch.Tensor:
+        """Lossless bf16 [M,K] (int16 storage); with exact=False escapes keep the "wrong" value."""
+        if out is None:
+            out = torch.empty((w.M, w.K), dtype=torch.int16, device=w.split_sm.device)
+        t = w.tensor(with_csr=exact)
+        check(self.lib.s12_decompress_async(C.byref(t), _ptr(out), _stream(stream)), "s12_decompress_async")
+        return out
+
+    def set_dependent_launch(self, enable: bool) -> bool:
+        return bool(self.lib.s12_set_dependent_launch(1 if enable else 0))
+
+    def device_status(self) -> int:
+        return int(self.lib.s12_device_status())
