@@ -90,6 +90,75 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+
+// ---------------------------------------------------------------------------
+// mbarrier + bulk-copy (TMA) wrappers.  Every wait is bounded: after kWaitSpins
+// failed polls the waiter records a site code in the device status word and
+// carries on, so a lost signal degrades to wrong results plus a status the
+// host can read, never to a hung GPU.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One poll: the thread may be suspended by the hardware for up to kWaitHintNs
+// before the instruction returns false.
+constexpr uint32_t kWaitHintNs = 1000000u;
+constexpr uint32_t kWaitSpins = 1u << 12;      // polls before giving up: seconds in total
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(kWaitHintNs) : "memory");
+    return ok != 0;
+}
+// Returns false (after flagging `site` in *status) when the wait gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* status, unsigned int site)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (uint32_t i = 1; i < kWaitSpins; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    if (status) atomicOr(status, site);
+    return false;
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
+// dst, src and bytes must be multiples of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// (a & b) | c in one instruction
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c)
+{
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 // ---------------------------------------------------------------------------
 // split12 decode, eight weights at a time
 // ---------------------------------------------------------------------------
@@ -118,6 +187,15 @@ __device__ __forceinline__ void decode8(uint32_t s_lo, uint32_t s_hi, uint32_t g
 {
     const uint32_t g8 = g >> 8;
     uint32_t e[4], m[4];
+    if (kMode == 0) {
+        // per pair: one AND, one multiply-add (exponent nibbles into place plus
+        // base), one byte permute, one (a & mask) | b
+        p[0] = and_or(prmt(s_lo, s_hi, 0xC480u), 0x807F807Fu, (g  & 0x000F000Fu) * 128u + base2);
+        p[1] = and_or(prmt(s_lo, s_hi, 0xD591u), 0x807F807Fu, (g  & 0x00F000F0u) * 8u + base2);
+        p[2] = and_or(prmt(s_lo, s_hi, 0xE6A2u), 0x807F807Fu, (g8 & 0x000F000Fu) * 128u + base2);
+        p[3] = and_or(prmt(s_lo, s_hi, 0xF7B3u), 0x807F807Fu, (g8 & 0x00F000F0u) * 8u + base2);
+        return;
+    }
     e[0] = (g  & 0x000F000Fu) << 7;
     e[1] = (g  & 0x00F000F0u) << 3;
     e[2] = (g8 & 0x000F000Fu) << 7;

@@ -368,6 +368,9 @@ gemv_generic_kernel(const __grid_constant__ GemvParams P, int mode)
     }
 }
 
+int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* outs, int mode,
+                    void* stream, const char* who, int* rc_out);
+
 static int env_int(const char* name, int dflt)
 {
     const char* e = getenv(name);
@@ -470,7 +473,14 @@ int gemv_dispatch(const GemvCall& c, void* stream)
     (mode == 0 ? launch_gemv_warps<0, NBV>(P, rg_total, stream)                              \
                : mode == 1 ? launch_gemv_warps<1, NBV>(P, rg_total, stream)                  \
                            : launch_gemv_warps<2, NBV>(P, rg_total, stream))
-    if (c.B == 1) return S12_GEMV_MODE(0);
+    if (c.B == 1) {
+        int rc = S12_OK;
+        void* outs[S12_MAX_MULTI];
+        for (int i = 0; i < c.nt; i++) outs[i] = c.o[i];
+        int used = gemv_stream_try(c.w, c.nt, c.x[0], outs, mode, stream, who, &rc);
+        if (used != 0) return rc;
+        return S12_GEMV_MODE(0);
+    }
     if (c.B <= 8) return S12_GEMV_MODE(1);
     return S12_GEMV_MODE(2);
 #undef S12_GEMV_MODE

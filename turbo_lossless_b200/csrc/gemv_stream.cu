@@ -1,0 +1,380 @@
+// B = 1 fused split12 decode + GEMV as a persistent, TMA-fed streaming kernel.
+//
+// The kernel is bound by HBM bandwidth (1.5 bytes per weight) and, for the
+// matrix sizes of a decode step, by how quickly every SM gets enough bytes in
+// flight and keeps them in flight until the last byte.  Design:
+//
+//   * One persistent CTA per SM.  A producer warp streams the packed weights
+//     into a ring of shared-memory stages with 1-D bulk copies
+//     (cp.async.bulk, completion counted on an mbarrier), so up to
+//     depth x 24 KB per SM are in flight without holding registers, and the
+//     stream does not pause between row blocks.
+//   * A stage holds one tile = 16 segments of 1024 columns (1 KB of sm and
+//     512 B of gr each).  The 16 segments are the 16 rows of the A operand of
+//     mma.sync.m16n8k16; which matrix row/column range a segment covers is a
+//     launch parameter: R rows x Q=16/R column chunks.  With R = 16 a tile is 16
+//     rows x 1024 columns; with R = 2 it is 2 rows x 8192 columns.  Segment i
+//     holds row (i mod R), chunk (i div R); the B operand's column n carries the
+//     activations of chunk n, so D[i][i div R] is segment i's dot product.
+//   * The Q chunks of one row are contiguous in memory, so a tile is fetched
+//     with one bulk copy per row and array: Q KB of sm, Q/2 KB of gr.  The copy
+//     engine needs roughly 70 cycles per bulk copy whatever its size (measured
+//     here: 1 KB copies reach 3.8 TB/s over 148 SMs, 4 KB copies 7.0 TB/s), so Q
+//     is taken as large as K allows.  Small R also gives many small work units
+//     (a 4096-row matrix becomes 1024 units for 148 SMs) with no cross-CTA
+//     reduction.
+//   * Sixteen consumer warps in two groups (alternate tiles); inside a group each
+//     warp takes 128 columns of every segment of the tile:
+//     16-byte shared loads, decode8 in registers (about 2 integer instructions
+//     per weight), tensor-core multiply-accumulate.  Rows are staggered in
+//     shared memory (16 B for sm, 64 B for gr) so that the 16-byte loads of
+//     neighbouring rows are bank-conflict free.
+//   * Two epilogue warps own the per-row-block tail, 16 rows at a time: they compute the escape
+//     correction sum_p (correct_p - wrong_p) * x[col_p] (second pass of the
+//     reference, nvidia_kernels.cu:271-290) from global memory while the
+//     consumers stream, then add the eight warps' partial sums and store.  The
+//     consumers never wait for global memory.
+//   * Under programmatic dependent launch the producer starts filling the ring
+//     immediately (weights are never written); only the consumers' staging of
+//     the activation vector and the epilogue's stores wait for the predecessor.
+//   * All mbarrier waits are bounded (common.cuh).
+#include "common.cuh"
+#include <cstdlib>
+
+namespace s12 {
+
+constexpr int kSegCols      = 1024;
+constexpr int kSmRowPad     = 16;       // stagger between rows of a tile in shared memory
+constexpr int kGrRowPad     = 64;
+constexpr int kGrBase       = 16 * 1024 + 16 * kSmRowPad;                // 16640
+constexpr int kStageBytes   = kGrBase + 16 * 512 + 16 * kGrRowPad;      // 25856 (worst case R = 16)
+constexpr int kGroups       = 2;        // consumer groups, working on alternate tiles
+constexpr int kGroupWarps   = 8;        // warps per group: 128 columns of every segment each
+constexpr int kConsumers    = kGroups * kGroupWarps;
+constexpr int kXChunkUnits  = kSegCols / 8 + 4;   // 16-byte units per activation chunk incl. 64 B stagger
+constexpr int kEpiWarps     = 2;
+constexpr int kStreamThreads = (kConsumers + 1 + kEpiWarps) * 32;
+constexpr int kRedSlots     = 24;       // row blocks whose partial sums may be pending
+constexpr int kMaxDepth     = 8;
+
+static_assert(kStageBytes % 128 == 0, "stage alignment");
+
+struct StreamTensor {
+    const uint8_t* sm;
+    const uint8_t* gr;
+    const int32_t* row_off;
+    const int32_t* cols;
+    const int16_t* correct;
+    const int16_t* wrong;
+    float* out;
+    int M;
+    uint32_t base2;
+    int blk_end;            // exclusive end of this tensor's row blocks
+};
+
+struct StreamParams {
+    StreamTensor t[S12_MAX_MULTI];
+    int nt;
+    const uint16_t* x;
+    int K;
+    int R, Q;               // rows per tile, column chunks per tile (R*Q == 16)
+    int tpr;                // tiles per row block = ceil(K / (Q*1024))
+    int depth;              // ring stages
+    int total_blocks;
+    unsigned int* status;
+};
+
+struct BlockRef { int ti; int r0; };
+
+__device__ __forceinline__ BlockRef locate_block(const StreamParams& P, int blk)
+{
+    int ti = 0;
+    while (ti + 1 < P.nt && blk >= P.t[ti].blk_end) ti++;
+    int first = ti ? P.t[ti - 1].blk_end : 0;
+    return BlockRef{ti, (blk - first) * P.R};
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+gemv_stream_kernel(const __grid_constant__ StreamParams P)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int depth = P.depth;
+    const int xunits = P.tpr * P.Q * kXChunkUnits;               // 16-byte units of permuted x
+    uint8_t* ring = smem;
+    uint4* xperm = reinterpret_cast<uint4*>(smem + (size_t)depth * kStageBytes);
+    float* red = reinterpret_cast<float*>(xperm + xunits);       // [kRedSlots][kConsumers][16]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + kRedSlots * kConsumers * 16);
+    const uint32_t bar_full = smem_addr(bars);                   // [kMaxDepth]
+    const uint32_t bar_empty = bar_full + 8 * kMaxDepth;         // [kMaxDepth]
+    const uint32_t bar_rowdone = bar_empty + 8 * kMaxDepth;      // [kRedSlots]
+    const uint32_t bar_redfree = bar_rowdone + 8 * kRedSlots;    // [kRedSlots]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kMaxDepth; i++) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, kGroupWarps); }
+        for (int i = 0; i < kRedSlots; i++) { mbar_init(bar_rowdone + 8 * i, P.tpr == 1 ? kGroupWarps : kConsumers); mbar_init(bar_redfree + 8 * i, 1); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    grid_launch_dependents();
+
+    // this CTA's contiguous range of row blocks
+    const int b0 = (int)(((long long)blockIdx.x * P.total_blocks) / gridDim.x);
+    const int b1 = (int)(((long long)(blockIdx.x + 1) * P.total_blocks) / gridDim.x);
+    const int nblocks = b1 - b0;
+    const int ntiles = nblocks * P.tpr;
+    const int K = P.K, R = P.R, Q = P.Q;
+
+    if (warp == kConsumers) {
+        // ------------------------------ producer ------------------------------
+        // lane l < R copies the sm part of row l of the tile, lane 16 + l its gr part.
+        // Everything a tile needs is kept incremental so that the producer's
+        // critical path per tile is one barrier poll, one arrive and one copy.
+        const int prow = lane & 15, is_gr = lane >> 4;
+        const uint32_t dst_off = is_gr ? kGrBase + prow * (Q * 512 + kGrRowPad) : prow * (Q * kSegCols + kSmRowPad);
+        const int tile_cols = Q * kSegCols;
+        int kt = 0, blk = b0, s = 0;
+        uint32_t wrap = 0;                                   // times the ring index wrapped
+        BlockRef br = locate_block(P, blk);
+        for (int i = 0; i < ntiles; i++) {
+            if (i >= depth) mbar_wait(bar_empty + 8 * s, (wrap - 1) & 1, P.status, 1u);
+            const StreamTensor& T = P.t[br.ti];
+            const int row = br.r0 + prow;
+            const int col0 = kt * tile_cols;
+            const int ncols = K - col0 > tile_cols ? tile_cols : K - col0;
+            const int nrows = T.M - br.r0 > R ? R : T.M - br.r0;
+            const bool valid = prow < nrows;
+            const uint32_t full = bar_full + 8 * s;
+            if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(nrows * (ncols + (ncols >> 1))));
+            __syncwarp();
+            if (valid) {
+                const size_t e0 = (size_t)row * K + col0;
+                const uint8_t* src = is_gr ? T.gr + (e0 >> 1) : T.sm + e0;
+                bulk_g2s(smem_addr(ring + (size_t)s * kStageBytes) + dst_off, src,
+                         (uint32_t)(is_gr ? (ncols >> 1) : ncols), full);
+            }
+            if (++s == depth) { s = 0; wrap++; }
+            if (++kt == P.tpr) { kt = 0; blk++; if (blk < b1) br = locate_block(P, blk); }
+        }
+        return;
+    }
+
+    grid_dependency_wait();
+
+    if (warp < kConsumers) {
+        // ------------------------------ consumers -----------------------------
+        // stage the activation vector, permuted so that a thread's B fragments
+        // for one 128-column step are four 16-byte units; chunks are staggered
+        // by 64 B so that lanes feeding different chunks hit different banks
+        for (int u = threadIdx.x; u < P.tpr * Q * (kSegCols / 8); u += kConsumers * 32) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (u * 8 < K) v = __ldg(reinterpret_cast<const uint4*>(P.x) + u);
+            uint4 pv;
+            pv.x = prmt(v.x, v.z, 0x5410u); pv.y = prmt(v.x, v.z, 0x7632u);
+            pv.z = prmt(v.y, v.w, 0x5410u); pv.w = prmt(v.y, v.w, 0x7632u);
+            const int c = u >> 7, uu = u & 127;
+            xperm[c * kXChunkUnits + (uu & ~15) + ((uu & 3) << 2) + ((uu >> 2) & 3)] = pv;
+        }
+        named_bar_sync(1, kConsumers * 32);
+
+        // two groups of eight warps work on alternate tiles; inside a group warp
+        // wi takes columns [wi*128, wi*128+128) of every segment
+        const int grp = warp / kGroupWarps, wi = warp % kGroupWarps;
+        const int g = lane >> 2, t4 = lane & 3;
+        const int qx = g % Q;                                // chunk whose activations this thread feeds
+        const int qA = g / R, qB = (g + 8) / R;              // chunk (= result column) of segments g, g+8
+        const int rA = g % R, rB = (g + 8) % R;              // tile row of segments g, g+8
+        const uint32_t offA = rA * (Q * kSegCols + kSmRowPad) + qA * kSegCols + wi * 128 + t4 * 32;
+        const uint32_t offB = rB * (Q * kSegCols + kSmRowPad) + qB * kSegCols + wi * 128 + t4 * 32;
+        const uint32_t goffA = kGrBase + rA * (Q * 512 + kGrRowPad) + qA * 512 + wi * 64 + t4 * 16;
+        const uint32_t goffB = kGrBase + rB * (Q * 512 + kGrRowPad) + qB * 512 + wi * 64 + t4 * 16;
+
+        float acc[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+        const int tpr = P.tpr;
+        int jb = grp / tpr, kt = grp % tpr;                  // block (within the CTA) and tile-in-block of tile i
+        int jb_loaded = -1;
+        uint32_t base2 = 0;
+        int s = grp % depth;
+        uint32_t wrap = grp / depth;
+        for (int i = grp; i < ntiles; i += kGroups) {
+            if (jb != jb_loaded) { base2 = P.t[locate_block(P, b0 + jb).ti].base2; jb_loaded = jb; }
+            mbar_wait(bar_full + 8 * s, wrap & 1, P.status, 2u);
+            const uint8_t* st = ring + (size_t)s * kStageBytes;
+            const uint4 a0 = *reinterpret_cast<const uint4*>(st + offA);
+            const uint4 a1 = *reinterpret_cast<const uint4*>(st + offA + 16);
+            const uint4 ga = *reinterpret_cast<const uint4*>(st + goffA);
+            const uint4 b0v = *reinterpret_cast<const uint4*>(st + offB);
+            const uint4 b1v = *reinterpret_cast<const uint4*>(st + offB + 16);
+            const uint4 gb = *reinterpret_cast<const uint4*>(st + goffB);
+            const uint4* xp = xperm + ((kt * Q + qx) * kXChunkUnits + wi * 16 + t4);
+            uint4 xq[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) xq[j] = xp[j * 4];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);   // stage data is in registers
+
+            const uint32_t sa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const uint32_t sb[8] = {b0v.x, b0v.y, b0v.z, b0v.w, b1v.x, b1v.y, b1v.z, b1v.w};
+            const uint32_t gaw[4] = {ga.x, ga.y, ga.z, ga.w};
+            const uint32_t gbw[4] = {gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t pa[4], pb[4];
+                decode8<kMode>(sa[2 * j], sa[2 * j + 1], gaw[j], base2, pa);
+                decode8<kMode>(sb[2 * j], sb[2 * j + 1], gbw[j], base2, pb);
+                mma_bf16_16816(acc[0], pa[0], pb[0], pa[1], pb[1], xq[j].x, xq[j].y);
+                mma_bf16_16816(acc[1], pa[2], pb[2], pa[3], pb[3], xq[j].z, xq[j].w);
+            }
+
+            // position of this warp's next tile
+            int jb_next = jb, kt_next = kt + kGroups;
+            while (kt_next >= tpr) { kt_next -= tpr; jb_next++; }
+            if (jb_next != jb || i + kGroups >= ntiles) {
+                // this warp's share of row block jb is complete: publish its 16 segment sums
+                const int slot = jb % kRedSlots;
+                if (jb >= kRedSlots) mbar_wait(bar_redfree + 8 * slot, ((jb / kRedSlots) - 1) & 1, P.status, 4u);
+                float* r = red + (slot * kConsumers + warp) * 16;
+                const float c0 = acc[0][0] + acc[1][0], c1 = acc[0][1] + acc[1][1];
+                const float c2 = acc[0][2] + acc[1][2], c3 = acc[0][3] + acc[1][3];
+                if (t4 == (qA >> 1)) r[g] = (qA & 1) ? c1 : c0;
+                if (t4 == (qB >> 1)) r[g + 8] = (qB & 1) ? c3 : c2;
+#pragma unroll
+                for (int a = 0; a < 2; a++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[a][j] = 0.f;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_rowdone + 8 * slot);
+            }
+            jb = jb_next; kt = kt_next;
+            s += kGroups;
+            if (s >= depth) { s -= depth; wrap++; }
+        }
+        return;
+    }
+
+    // ------------------------------ epilogue ----------------------------------
+    // 16 rows (= 16/R consecutive row blocks) per pass; two lanes per row walk
+    // the row's escapes.  The corrections are computed before waiting for the
+    // consumers, so their global-memory latency overlaps the streaming.
+    const int e = warp - kConsumers - 1;
+    const int gb = 16 / R;                                   // blocks per pass
+    const int rho = lane & 15, sub = lane >> 4;
+    const int ngroups = (nblocks + gb - 1) / gb;
+    for (int grp = e; grp < ngroups; grp += kEpiWarps) {
+        const int jb = grp * gb + rho / R;                   // this lane's block (index within the CTA)
+        const bool have = jb < nblocks;
+        BlockRef br = locate_block(P, b0 + (have ? jb : nblocks - 1));
+        const StreamTensor& T = P.t[br.ti];
+        const int row = br.r0 + rho % R;
+        float corr = 0.f;
+        if (have && T.row_off != nullptr && row < T.M) {
+            const int lo = T.row_off[row], hi = T.row_off[row + 1];
+            for (int p = lo + sub; p < hi; p += 2) {
+                float dv = bf16_bits_to_float((uint16_t)T.correct[p]);
+                if (kMode != 2) dv -= bf16_bits_to_float((uint16_t)T.wrong[p]);
+                corr += dv * bf16_bits_to_float(P.x[T.cols[p]]);
+            }
+        }
+        corr += __shfl_xor_sync(0xFFFFFFFFu, corr, 16);
+        const int jfirst = grp * gb;
+        const int jlast = (jfirst + gb < nblocks ? jfirst + gb : nblocks) - 1;
+        for (int j = jfirst; j <= jlast; j++)
+            mbar_wait(bar_rowdone + 8 * (j % kRedSlots), (j / kRedSlots) & 1, P.status, 8u);
+        if (lane < 16 && have) {
+            const float* r = red + (jb % kRedSlots) * kConsumers * 16;
+            float v = corr;
+            // with one tile per row block only the group that owned the tile contributed
+            const int w0 = P.tpr == 1 ? (jb % kGroups) * kGroupWarps : 0;
+            const int w1 = P.tpr == 1 ? w0 + kGroupWarps : kConsumers;
+            for (int w = w0; w < w1; w++)
+                for (int q = 0; q < Q; q++) v += r[w * 16 + q * R + rho % R];
+            if (row < T.M) T.out[row] = v;
+        }
+        __syncwarp();
+        if (lane == 0)
+            for (int j = jfirst; j <= jlast; j++) mbar_arrive(bar_redfree + 8 * (j % kRedSlots));
+    }
+}
+
+static int env_int2(const char* name, int dflt)
+{
+    const char* e = getenv(name);
+    return (e && *e) ? atoi(e) : dflt;
+}
+
+// Returns 1 and launches when the streaming kernel applies; 0 when the caller
+// should use the register-pipelined kernel; negative on error.
+int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* outs, int mode,
+                    void* stream, const char* who, int* rc_out)
+{
+    const int impl = env_int2("S12_GEMV_IMPL", 1);              // 0: never, 1: auto (tuning/test knobs)
+    const int force_r = env_int2("S12_GEMV_R", 0);
+    const int force_depth = env_int2("S12_GEMV_DEPTH", 0);
+    if (!impl) return 0;
+    const int K = w[0].K;
+    if (K % 32 != 0 || K < 128) return 0;
+    long long rows = 0;
+    for (int i = 0; i < nt; i++) rows += w[i].M;
+    if (rows * (long long)K < (1ll << 20) && impl != 2) return 0;   // tiny: not worth a persistent launch
+
+    const int sms = sm_count();
+    // Column chunks per tile: as many as K holds (up to 8), because the copy
+    // engine's cost is per bulk copy and a row's chunks travel as one copy.
+    int Qsel = 1;
+    while (Qsel < 8 && 2 * Qsel * kSegCols <= K) Qsel <<= 1;
+    int R = 16 / Qsel;
+    if (force_r == 2 || force_r == 4 || force_r == 8 || force_r == 16) R = force_r;
+    const int Q = 16 / R;
+    StreamParams P = {};
+    P.nt = nt; P.x = (const uint16_t*)act; P.K = K; P.R = R; P.Q = Q;
+    P.tpr = (K + Q * kSegCols - 1) / (Q * kSegCols);
+    int blocks = 0;
+    for (int i = 0; i < nt; i++) {
+        StreamTensor& t = P.t[i];
+        const bool csr = w[i].row_off && w[i].cols && w[i].correct && w[i].wrong;
+        t.sm = w[i].sm; t.gr = w[i].gr;
+        t.row_off = csr ? w[i].row_off : nullptr; t.cols = w[i].cols; t.correct = w[i].correct; t.wrong = w[i].wrong;
+        t.out = (float*)outs[i]; t.M = w[i].M; t.base2 = make_base2(w[i].base_exp);
+        blocks += (w[i].M + R - 1) / R;
+        t.blk_end = blocks;
+    }
+    P.total_blocks = blocks;
+    P.status = device_status_word();
+
+    const size_t fixed = (size_t)P.tpr * Q * kXChunkUnits * 16 + kRedSlots * kConsumers * 16 * sizeof(float) +
+                         8 * (2 * kMaxDepth + 2 * kRedSlots);
+    static int max_smem = 0;
+    if (!max_smem) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    }
+    int depth = (int)(((size_t)max_smem - fixed) / kStageBytes);
+    if ((size_t)max_smem < fixed + 2 * (size_t)kStageBytes) return 0;   // K too large for this layout
+    if (depth > kMaxDepth) depth = kMaxDepth;
+    if (force_depth >= 2 && force_depth < depth) depth = force_depth;
+    P.depth = depth;
+    const size_t smem = fixed + (size_t)depth * kStageBytes;
+
+    auto kern = mode == 0 ? gemv_stream_kernel<0> : mode == 1 ? gemv_stream_kernel<1> : gemv_stream_kernel<2>;
+    static bool attr_set[64][3];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = (dev < 0 || dev >= 64) ? 0 : dev;
+    if (!attr_set[dev][mode]) {
+        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem), who);
+        if (rc) { *rc_out = rc; return -1; }
+        attr_set[dev][mode] = true;
+    }
+    const int grid = blocks < sms ? blocks : sms;
+    *rc_out = launch(kern, dim3(grid), dim3(kStreamThreads), smem, stream, who, P);
+    return *rc_out == S12_OK ? 1 : -1;
+}
+
+}  // namespace s12
