@@ -228,6 +228,31 @@ int64_t s12_host_shard_cols(const S12Tensor* src, int c0, int c1,
                             uint8_t* sm, uint8_t* gr, int32_t* row_off,
                             int32_t* cols, int16_t* correct, int16_t* wrong);
 
+/* =========================================================================
+ * 4. Device-side packer (bit-identical to the reference's CPU packer)
+ * ========================================================================= */
+
+/* 256-bin histogram of the bf16 exponent field of `count` values into
+ * hist256 (device, 256 x uint64), first half of split12_find_base_exp
+ * (split12_pack.c:18-25). */
+int s12_pack_histogram_async(const void* bf16, int64_t count, void* hist256, void* stream);
+
+/* HOST: the window search of split12_find_base_exp (split12_pack.c:27-37)
+ * over a histogram copied back from the device.  Returns base_exp. */
+int s12_pack_find_base_exp_host(const uint64_t* hist256);
+
+/* First pass of pack_split12 (split12_pack.c:76-104): writes sm[M*K],
+ * gr[M*K/2] and the CSR row pointers row_off[M+1] (inclusive prefix sums of the
+ * per-row escape counts).  row_off[M] is the number of escapes the caller must
+ * provide room for before the second pass. */
+int s12_pack_async(const void* bf16, int M, int K, int base_exp, void* sm, void* gr,
+                   void* row_off, void* stream);
+
+/* Second pass (split12_pack.c:106-124): cols / correct / wrong in ascending
+ * column order within each row. */
+int s12_pack_fill_async(const void* bf16, int M, int K, int base_exp, const void* row_off,
+                        void* cols, void* correct, void* wrong, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

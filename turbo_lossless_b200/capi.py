@@ -52,6 +52,10 @@ SIGNATURES = {
     "s12_host_build_escape_table": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
     "s12_host_shard_rows": (C.c_int64, [C.POINTER(S12Tensor), _i, _i] + [_vp] * 6),
     "s12_host_shard_cols": (C.c_int64, [C.POINTER(S12Tensor), _i, _i] + [_vp] * 6),
+    "s12_pack_histogram_async": (_i, [_vp, C.c_int64, _vp, _vp]),
+    "s12_pack_find_base_exp_host": (_i, [_vp]),
+    "s12_pack_async": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "s12_pack_fill_async": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }
 
 _lib = None

@@ -16,19 +16,18 @@
 //     rows x 1024 columns; with R = 2 it is 2 rows x 8192 columns.  Segment i
 //     holds row (i mod R), chunk (i div R); the B operand's column n carries the
 //     activations of chunk n, so D[i][i div R] is segment i's dot product.
-//   * The Q chunks of one row are contiguous in memory, so a tile is fetched
-//     with one bulk copy per row and array: Q KB of sm, Q/2 KB of gr.  The copy
-//     engine needs roughly 70 cycles per bulk copy whatever its size (measured
-//     here: 1 KB copies reach 3.8 TB/s over 148 SMs, 4 KB copies 7.0 TB/s), so Q
-//     is taken as large as K allows.  Small R also gives many small work units
+//   * A stage is the dense image of its tile, so the Q chunks of a row travel
+//     as one bulk copy (Q KB of sm, Q/2 KB of gr) and, when the tile spans whole
+//     rows, the entire tile as two copies (16 KB + 8 KB).  The copy engine needs
+//     roughly 70 cycles per bulk copy whatever its size (measured here: 1 KB
+//     copies reach 3.8 TB/s over 148 SMs, 4 KB copies 7.0 TB/s), so Q is taken
+//     as large as K allows.  Small R also gives many small work units
 //     (a 4096-row matrix becomes 1024 units for 148 SMs) with no cross-CTA
 //     reduction.
 //   * Sixteen consumer warps in two groups (alternate tiles); inside a group each
 //     warp takes 128 columns of every segment of the tile:
 //     16-byte shared loads, decode8 in registers (about 2 integer instructions
-//     per weight), tensor-core multiply-accumulate.  Rows are staggered in
-//     shared memory (16 B for sm, 64 B for gr) so that the 16-byte loads of
-//     neighbouring rows are bank-conflict free.
+//     per weight), tensor-core multiply-accumulate.
 //   * Two epilogue warps own the per-row-block tail, 16 rows at a time: they compute the escape
 //     correction sum_p (correct_p - wrong_p) * x[col_p] (second pass of the
 //     reference, nvidia_kernels.cu:271-290) from global memory while the
@@ -44,10 +43,8 @@
 namespace s12 {
 
 constexpr int kSegCols      = 1024;
-constexpr int kSmRowPad     = 16;       // stagger between rows of a tile in shared memory
-constexpr int kGrRowPad     = 64;
-constexpr int kGrBase       = 16 * 1024 + 16 * kSmRowPad;                // 16640
-constexpr int kStageBytes   = kGrBase + 16 * 512 + 16 * kGrRowPad;      // 25856 (worst case R = 16)
+constexpr int kGrBase       = 16 * kSegCols;                             // gr part of a stage
+constexpr int kStageBytes   = kGrBase + 16 * (kSegCols / 2);             // 24576: dense image of the tile
 constexpr int kGroups       = 2;        // consumer groups, working on alternate tiles
 constexpr int kGroupWarps   = 8;        // warps per group: 128 columns of every segment each
 constexpr int kConsumers    = kGroups * kGroupWarps;
@@ -86,6 +83,20 @@ struct StreamParams {
 
 struct BlockRef { int ti; int r0; };
 
+#ifdef S12_TRACE
+// Development aid: per-CTA timestamps (ns) of kernel phases.
+__device__ unsigned long long g_trace[148 * 8];
+__device__ __forceinline__ unsigned long long now_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define S12_STAMP(slot) do { if (lane == 0 && blockIdx.x < 148) g_trace[blockIdx.x * 8 + (slot)] = now_ns(); } while (0)
+#else
+#define S12_STAMP(slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ BlockRef locate_block(const StreamParams& P, int blk)
 {
     int ti = 0;
@@ -111,11 +122,15 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
     const uint32_t bar_redfree = bar_rowdone + 8 * kRedSlots;    // [kRedSlots]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kMaxDepth; i++) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, kGroupWarps); }
-        for (int i = 0; i < kRedSlots; i++) { mbar_init(bar_rowdone + 8 * i, P.tpr == 1 ? kGroupWarps : kConsumers); mbar_init(bar_redfree + 8 * i, 1); }
-        mbar_fence_init();
+    if (warp == 0) S12_STAMP(0);
+    if (threadIdx.x < kMaxDepth) {
+        mbar_init(bar_full + 8 * threadIdx.x, 1);
+        mbar_init(bar_empty + 8 * threadIdx.x, kGroupWarps);
+    } else if (threadIdx.x >= 32 && threadIdx.x < 32 + kRedSlots) {
+        mbar_init(bar_rowdone + 8 * (threadIdx.x - 32), P.tpr == 1 ? kGroupWarps : kConsumers);
+        mbar_init(bar_redfree + 8 * (threadIdx.x - 32), 1);
     }
+    mbar_fence_init();
     __syncthreads();
     grid_launch_dependents();
 
@@ -128,35 +143,41 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
 
     if (warp == kConsumers) {
         // ------------------------------ producer ------------------------------
-        // lane l < R copies the sm part of row l of the tile, lane 16 + l its gr part.
+        // A stage is the dense image of the tile: R rows of Q*1024 columns.  When
+        // a tile spans whole rows (K == Q*1024) its rows are adjacent in memory
+        // and lanes 0 / 16 fetch the sm / gr part with one copy each; otherwise
+        // lane l < R copies row l's sm part and lane 16 + l its gr part.
         // Everything a tile needs is kept incremental so that the producer's
         // critical path per tile is one barrier poll, one arrive and one copy.
         const int prow = lane & 15, is_gr = lane >> 4;
-        const uint32_t dst_off = is_gr ? kGrBase + prow * (Q * 512 + kGrRowPad) : prow * (Q * kSegCols + kSmRowPad);
         const int tile_cols = Q * kSegCols;
+        const bool whole_rows = K == tile_cols;
+        const uint32_t dst_off = is_gr ? kGrBase + prow * (tile_cols >> 1) : prow * tile_cols;
         int kt = 0, blk = b0, s = 0;
         uint32_t wrap = 0;                                   // times the ring index wrapped
         BlockRef br = locate_block(P, blk);
         for (int i = 0; i < ntiles; i++) {
             if (i >= depth) mbar_wait(bar_empty + 8 * s, (wrap - 1) & 1, P.status, 1u);
             const StreamTensor& T = P.t[br.ti];
-            const int row = br.r0 + prow;
             const int col0 = kt * tile_cols;
             const int ncols = K - col0 > tile_cols ? tile_cols : K - col0;
             const int nrows = T.M - br.r0 > R ? R : T.M - br.r0;
-            const bool valid = prow < nrows;
             const uint32_t full = bar_full + 8 * s;
             if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(nrows * (ncols + (ncols >> 1))));
             __syncwarp();
-            if (valid) {
-                const size_t e0 = (size_t)row * K + col0;
+            const int ncopy_rows = whole_rows ? 1 : nrows;   // rows this tile is copied in
+            if (prow < ncopy_rows) {
+                const size_t e0 = (size_t)(br.r0 + prow) * K + col0;
                 const uint8_t* src = is_gr ? T.gr + (e0 >> 1) : T.sm + e0;
+                const uint32_t elems = whole_rows ? (uint32_t)(nrows * K) : (uint32_t)ncols;
                 bulk_g2s(smem_addr(ring + (size_t)s * kStageBytes) + dst_off, src,
-                         (uint32_t)(is_gr ? (ncols >> 1) : ncols), full);
+                         is_gr ? (elems >> 1) : elems, full);
             }
             if (++s == depth) { s = 0; wrap++; }
             if (++kt == P.tpr) { kt = 0; blk++; if (blk < b1) br = locate_block(P, blk); }
+            if (i == 0) S12_STAMP(1);
         }
+        S12_STAMP(6);
         return;
     }
 
@@ -173,10 +194,15 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             uint4 pv;
             pv.x = prmt(v.x, v.z, 0x5410u); pv.y = prmt(v.x, v.z, 0x7632u);
             pv.z = prmt(v.y, v.w, 0x5410u); pv.w = prmt(v.y, v.w, 0x7632u);
-            const int c = u >> 7, uu = u & 127;
-            xperm[c * kXChunkUnits + (uu & ~15) + ((uu & 3) << 2) + ((uu >> 2) & 3)] = pv;
+            // unit uu of a 128-column step (16 units of 8 columns): thread t4 reads
+            // units 2*t4, 2*t4+1 (low run) and 8+2*t4, 8+2*t4+1 (high run) as its
+            // loads j = 0..3, each from position j*4 + t4
+            const int c = u >> 7, uu = u & 127, w16 = uu & 15;
+            const int pos = (((w16 >> 3) << 1) + (w16 & 1)) * 4 + ((w16 & 7) >> 1);
+            xperm[c * kXChunkUnits + (uu & ~15) + pos] = pv;
         }
         named_bar_sync(1, kConsumers * 32);
+        if (warp == 0) S12_STAMP(2);
 
         // two groups of eight warps work on alternate tiles; inside a group warp
         // wi takes columns [wi*128, wi*128+128) of every segment
@@ -185,10 +211,18 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         const int qx = g % Q;                                // chunk whose activations this thread feeds
         const int qA = g / R, qB = (g + 8) / R;              // chunk (= result column) of segments g, g+8
         const int rA = g % R, rB = (g + 8) % R;              // tile row of segments g, g+8
-        const uint32_t offA = rA * (Q * kSegCols + kSmRowPad) + qA * kSegCols + wi * 128 + t4 * 32;
-        const uint32_t offB = rB * (Q * kSegCols + kSmRowPad) + qB * kSegCols + wi * 128 + t4 * 32;
-        const uint32_t goffA = kGrBase + rA * (Q * 512 + kGrRowPad) + qA * 512 + wi * 64 + t4 * 16;
-        const uint32_t goffB = kGrBase + rB * (Q * 512 + kGrRowPad) + qB * 512 + wi * 64 + t4 * 16;
+        // Inside its warp's 128-column window a thread owns two runs of 16
+        // columns: [t4*16, +16) and [64 + t4*16, +16).  All segments start on the
+        // same bank, so lanes with odd g fetch the two runs in the opposite
+        // order (and swap them back in registers): in every 8-lane phase of a
+        // 16-byte load the even-g lanes then hit the low 64 bytes of the window
+        // and the odd-g lanes the high 64 bytes.
+        const uint32_t odd = g & 1;
+        const uint32_t offA = (rA * Q + qA) * kSegCols + wi * 128 + t4 * 16;
+        const uint32_t offB = (rB * Q + qB) * kSegCols + wi * 128 + t4 * 16;
+        const uint32_t goffA = kGrBase + (rA * Q + qA) * (kSegCols / 2) + wi * 64 + t4 * 8;
+        const uint32_t goffB = kGrBase + (rB * Q + qB) * (kSegCols / 2) + wi * 64 + t4 * 8;
+        const uint32_t first = odd * 64, second = 64 - first;
 
         float acc[2][4];
 #pragma unroll
@@ -205,13 +239,16 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         for (int i = grp; i < ntiles; i += kGroups) {
             if (jb != jb_loaded) { base2 = P.t[locate_block(P, b0 + jb).ti].base2; jb_loaded = jb; }
             mbar_wait(bar_full + 8 * s, wrap & 1, P.status, 2u);
+            if (warp == 0 && i == 0) S12_STAMP(3);
             const uint8_t* st = ring + (size_t)s * kStageBytes;
-            const uint4 a0 = *reinterpret_cast<const uint4*>(st + offA);
-            const uint4 a1 = *reinterpret_cast<const uint4*>(st + offA + 16);
-            const uint4 ga = *reinterpret_cast<const uint4*>(st + goffA);
-            const uint4 b0v = *reinterpret_cast<const uint4*>(st + offB);
-            const uint4 b1v = *reinterpret_cast<const uint4*>(st + offB + 16);
-            const uint4 gb = *reinterpret_cast<const uint4*>(st + goffB);
+            const uint4 af = *reinterpret_cast<const uint4*>(st + offA + first);
+            const uint4 as = *reinterpret_cast<const uint4*>(st + offA + second);
+            const uint2 gaf = *reinterpret_cast<const uint2*>(st + goffA + (first >> 1));
+            const uint2 gas = *reinterpret_cast<const uint2*>(st + goffA + (second >> 1));
+            const uint4 bf = *reinterpret_cast<const uint4*>(st + offB + first);
+            const uint4 bs = *reinterpret_cast<const uint4*>(st + offB + second);
+            const uint2 gbf = *reinterpret_cast<const uint2*>(st + goffB + (first >> 1));
+            const uint2 gbs = *reinterpret_cast<const uint2*>(st + goffB + (second >> 1));
             const uint4* xp = xperm + ((kt * Q + qx) * kXChunkUnits + wi * 16 + t4);
             uint4 xq[4];
 #pragma unroll
@@ -219,10 +256,14 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);   // stage data is in registers
 
+            const uint4 a0 = odd ? as : af, a1 = odd ? af : as;      // low run, high run
+            const uint4 b0v = odd ? bs : bf, b1v = odd ? bf : bs;
+            const uint2 ga0 = odd ? gas : gaf, ga1 = odd ? gaf : gas;
+            const uint2 gb0 = odd ? gbs : gbf, gb1 = odd ? gbf : gbs;
             const uint32_t sa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const uint32_t sb[8] = {b0v.x, b0v.y, b0v.z, b0v.w, b1v.x, b1v.y, b1v.z, b1v.w};
-            const uint32_t gaw[4] = {ga.x, ga.y, ga.z, ga.w};
-            const uint32_t gbw[4] = {gb.x, gb.y, gb.z, gb.w};
+            const uint32_t gaw[4] = {ga0.x, ga0.y, ga1.x, ga1.y};
+            const uint32_t gbw[4] = {gb0.x, gb0.y, gb1.x, gb1.y};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 uint32_t pa[4], pb[4];
@@ -255,6 +296,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             s += kGroups;
             if (s >= depth) { s -= depth; wrap++; }
         }
+        if (warp == 0) S12_STAMP(4);
         return;
     }
 
@@ -300,6 +342,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         if (lane == 0)
             for (int j = jfirst; j <= jlast; j++) mbar_arrive(bar_redfree + 8 * (j % kRedSlots));
     }
+    if (e == 0) S12_STAMP(5);
 }
 
 static int env_int2(const char* name, int dflt)

@@ -127,6 +127,42 @@ class CompressedWeight:
             ro = co = cv = wv = None
         return cls.from_host(M, K, base_exp, sm, gr, ro, co, cv, wv, device=device, **kw)
 
+    @classmethod
+    def pack_on_device(cls, w_bf16: torch.Tensor, base_exp: Optional[int] = None,
+                       escape_table: bool = False) -> "CompressedWeight":
+        """Packs a bf16 [M,K] tensor that already lives on the device with the library's packer
+        kernels (same bytes as split12_find_base_exp + pack_split12 of the reference)."""
+        assert w_bf16.is_cuda and w_bf16.dim() == 2 and w_bf16.dtype in (torch.bfloat16, torch.int16)
+        lib = capi.load()
+        w = w_bf16.contiguous()
+        M, K = w.shape
+        dev = w.device
+        st = _stream()
+        if base_exp is None:
+            hist = torch.empty(256, dtype=torch.int64, device=dev)
+            check(lib.s12_pack_histogram_async(w.data_ptr(), M * K, hist.data_ptr(), st), "s12_pack_histogram_async")
+            h = np.ascontiguousarray(hist.cpu().numpy().astype(np.uint64))
+            base_exp = int(lib.s12_pack_find_base_exp_host(h.ctypes.data))
+        sm = torch.empty(M * K, dtype=torch.uint8, device=dev)
+        gr = torch.empty(M * K // 2, dtype=torch.uint8, device=dev)
+        row_off = torch.empty(M + 1, dtype=torch.int32, device=dev)
+        check(lib.s12_pack_async(w.data_ptr(), M, K, base_exp, sm.data_ptr(), gr.data_ptr(), row_off.data_ptr(), st),
+              "s12_pack_async")
+        npat = int(row_off[-1].item())
+        out = cls(M=M, K=K, base_exp=base_exp, split_sm=sm, split_gr=gr, num_patches=npat)
+        if npat > 0:
+            cols = torch.empty(npat, dtype=torch.int32, device=dev)
+            correct = torch.empty(npat, dtype=torch.int16, device=dev)
+            wrong = torch.empty(npat, dtype=torch.int16, device=dev)
+            check(lib.s12_pack_fill_async(w.data_ptr(), M, K, base_exp, row_off.data_ptr(), cols.data_ptr(),
+                                          correct.data_ptr(), wrong.data_ptr(), st), "s12_pack_fill_async")
+            out.row_offsets, out.patch_cols, out.patch_correct, out.patch_wrong = row_off, cols, correct, wrong
+            if escape_table:
+                host = cls.from_host(M, K, base_exp, sm.cpu().numpy(), gr.cpu().numpy(), row_off.cpu().numpy(),
+                                     cols.cpu().numpy(), correct.cpu().numpy(), wrong.cpu().numpy(), device=dev)
+                return host
+        return out
+
     # -- views -----------------------------------------------------------------
     def tensor(self, with_csr: bool = True) -> S12Tensor:
         t = S12Tensor()
