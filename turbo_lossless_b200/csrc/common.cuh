@@ -119,8 +119,8 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 // One poll: the thread may be suspended by the hardware for up to kWaitHintNs
 // before the instruction returns false.
-constexpr uint32_t kWaitHintNs = 1000000u;
-constexpr uint32_t kWaitSpins = 1u << 12;      // polls before giving up: seconds in total
+constexpr uint32_t kWaitHintNs = 500000u;
+constexpr uint32_t kWaitSpins = 1u << 12;      // polls before giving up: about two seconds in total
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -130,14 +130,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity), "r"(kWaitHintNs) : "memory");
     return ok != 0;
 }
-// Returns false (after flagging `site` in *status) when the wait gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* status, unsigned int site)
+// Returns false when the wait gave up: `site` is then ORed into *status and
+// *cta_abort (shared memory) is raised, which makes every later wait of the CTA
+// give up after a single poll, so a lost signal costs seconds, not hours.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* status, unsigned int site,
+                                          volatile int* cta_abort = nullptr)
 {
     if (mbar_try_wait(bar, parity)) return true;
 #pragma unroll 1
-    for (uint32_t i = 1; i < kWaitSpins; i++)
+    for (uint32_t i = 1; i < kWaitSpins; i++) {
+        if (cta_abort && *cta_abort) return false;
         if (mbar_try_wait(bar, parity)) return true;
+    }
     if (status) atomicOr(status, site);
+    if (cta_abort) *cta_abort = 1;
     return false;
 }
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.

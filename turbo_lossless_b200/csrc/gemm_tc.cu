@@ -1,10 +1,524 @@
-// tcgen05 / TMEM decode + GEMM (placeholder until the kernel lands: reports
-// "not supported" so the dispatcher uses the GEMV family).
+// Batched split12 decode + GEMM on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory), B > 16.
+//
+//   C[b, m] = sum_k W[m, k] * X[b, k]      fp32 out[b*out_stride + m]
+//
+// Roles inside one persistent CTA (one CTA per SM, 16 warps):
+//   warp 0       producer: TMA tensor-map loads of the raw packed tile
+//                (128 rows x 64 sm bytes, 128 x 32 gr bytes) and of the
+//                activation tile (BN sequences x 64 k, 128-byte swizzle)
+//   warp 1       owns tensor memory (alloc/dealloc) and issues the MMAs from
+//                one thread: per 64-column block four tcgen05.mma
+//                (M=128, N=BN, K=16, bf16 x bf16 -> fp32 in TMEM)
+//   warps 4-11   decode: raw bytes -> bf16 (decode8, escapes patched from the
+//                CSR list when the tensor brings one) written into the
+//                K-major, 128-byte-swizzled A tile the MMA descriptor expects,
+//                then fence.proxy.async + mbarrier arrive
+//   warps 12-15  epilogue: tcgen05.ld of the finished accumulator (double
+//                buffered in TMEM, so it overlaps the next tile's main loop),
+//                coalesced fp32 stores (32 consecutive m per store)
+//   warps 2-3    idle
+//
+// Work is split stream-K style: the (M tiles x N tiles x K blocks) iteration
+// space is cut into equal contiguous ranges, one per CTA, so a 4096-row
+// projection (32 tiles) still occupies all 148 SMs.  A CTA that covers only
+// part of a tile's K range writes its partial accumulator to a workspace; the
+// last contributor of a tile (an atomic counter, no waiting) adds the partials
+// in a fixed order and stores the result, so the output is deterministic.
+//
+// Escapes: with the CSR list the decoded weights are exact inside the MMA;
+// without it they keep the reference's "wrong" value (exponent base_exp), which
+// is what the engine's two-pass path expects before nv_launch_patches_batch.
+//
+// Replaces split12_fused_gemm / _v2 / _v3 (split12_gemm.cuh:99-288,
+// split12_gemm_v2.cuh:86-240, split12_gemm_v3.cuh:111-253 of the reference,
+// mma.sync kernels) and the decode + library-GEMM path
+// (nvidia_kernels.cu:533-584).
 #include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+
 namespace s12 {
-int gemm_tc_supported(const S12Tensor*, int, int, int) { return 0; }
-int gemm_tc_launch(const S12Tensor*, const void*, int, void*, int, int, void*, const char* who)
+
+constexpr int kTM = 128;                 // weight rows per tile
+constexpr int kTK = 64;                  // columns per K block
+constexpr int kRawStages = 4;
+constexpr int kOpStages = 3;             // decoded-A and activation stages
+constexpr int kRawBytes = kTM * kTK + kTM * kTK / 2;      // 12288
+constexpr int kABytes = kTM * kTK * 2;                    // 16384
+constexpr int kDecodeWarps = 16;         // 512 threads: one (row, 16-column chunk) each per K block
+constexpr int kFirstDecodeWarp = 4, kFirstEpiWarp = kFirstDecodeWarp + kDecodeWarps;
+constexpr int kGemmThreads = (kFirstEpiWarp + 4) * 32;
+
+struct GemmParams {
+    const int32_t* row_off;     // null: escapes stay "wrong"
+    const int32_t* cols;
+    const int16_t* correct;
+    float* out;
+    float* ws;                  // [grid][2][BN][128] partial accumulators
+    unsigned int* status;
+    int M, K, B, out_stride;
+    int BN;                     // sequences per tile (multiple of 16, <= 256)
+    int n_mtiles, n_ntiles, KB; // KB = K blocks per tile
+    uint32_t base2;
+    int neg_base;               // base_exp < 0: decode mode 1
+    uint32_t tmem_cols;
+};
+
+// ----------------------------------------------------------------------------
+// tcgen05 / TMA wrappers
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
 {
-    return fail(S12_ERR_UNSUPPORTED, "%s: tensor-core path not built", who);
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, fp32 accumulate
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);          // start address
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                          // descriptor version
+    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------
+// schedule shared by all roles: this CTA's contiguous range [lo, hi) of
+// (tile, K block) iterations, walked tile by tile; tile t covers iterations
+// [t*KB, (t+1)*KB)
+// ----------------------------------------------------------------------------
+struct Range { int lo, hi; };
+__host__ __device__ __forceinline__ Range cta_range(long long T, int G, int cta)
+{
+    return Range{(int)(T * cta / G), (int)(T * (cta + 1) / G)};
+}
+
+// One decode thread owns one (row, 16-column chunk) of every K block.
+template <int kMode>
+__device__ __forceinline__ void decode_item(const uint8_t* raw, uint8_t* A, int item, uint32_t off_lo, uint32_t off_hi,
+                                            uint32_t base2, const GemmParams& P, int m0, int k0)
+{
+    const uint4 s = *reinterpret_cast<const uint4*>(raw + item * 16);
+    const uint2 g = *reinterpret_cast<const uint2*>(raw + kTM * kTK + item * 8);
+    uint32_t p[4], lo[4], hi[4];
+    decode8<kMode>(s.x, s.y, g.x, base2, p);
+    lo[0] = prmt(p[0], p[1], 0x5410u); lo[1] = prmt(p[2], p[3], 0x5410u);
+    lo[2] = prmt(p[0], p[1], 0x7632u); lo[3] = prmt(p[2], p[3], 0x7632u);
+    decode8<kMode>(s.z, s.w, g.y, base2, p);
+    hi[0] = prmt(p[0], p[1], 0x5410u); hi[1] = prmt(p[2], p[3], 0x5410u);
+    hi[2] = prmt(p[0], p[1], 0x7632u); hi[3] = prmt(p[2], p[3], 0x7632u);
+    *reinterpret_cast<uint4*>(A + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    *reinterpret_cast<uint4*>(A + off_hi) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    if (P.row_off != nullptr && (zero_nibbles(g.x) | zero_nibbles(g.y))) {
+        const int r = item >> 2, c = item & 3, sw = r & 7;
+        const int row = m0 + r;
+        if (row < P.M) {
+            const int lo0 = P.row_off[row], hi0 = P.row_off[row + 1];
+#pragma unroll 1
+            for (int i = 0; i < 16; i++) {
+                const uint32_t gw = i < 8 ? g.x : g.y;
+                if (((gw >> (4 * (i & 7))) & 0xFu) != 0u) continue;
+                const int col = k0 + c * 16 + i;
+                int a = lo0, b = hi0;
+                while (a < b) { int mid = (a + b) >> 1; if (P.cols[mid] < col) a = mid + 1; else b = mid; }
+                if (a < hi0 && P.cols[a] == col) {
+                    const int kc = c * 16 + i;              // column inside the K block
+                    *reinterpret_cast<uint16_t*>(A + r * 128 + (((kc >> 3) ^ sw) << 4) + (kc & 7) * 2) = (uint16_t)P.correct[a];
+                }
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant__ CUtensorMap map_gr,
+               const __grid_constant__ CUtensorMap map_x, const __grid_constant__ GemmParams P)
+{
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    // swizzled operand tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    const int BN = P.BN;
+    const uint32_t xbytes = (uint32_t)BN * 128u;
+    uint8_t* raw = smem;                                         // [kRawStages][12288]
+    uint8_t* Abuf = raw + kRawStages * kRawBytes;                // [kOpStages][16384]
+    uint8_t* Xbuf = Abuf + kOpStages * kABytes;                  // [kOpStages][BN*128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Xbuf + (size_t)kOpStages * xbytes);
+    const uint32_t b_rawfull = smem_addr(bars);                  // [kRawStages]
+    const uint32_t b_rawempty = b_rawfull + 8 * kRawStages;      // [kRawStages]
+    const uint32_t b_afull = b_rawempty + 8 * kRawStages;        // [kOpStages]
+    const uint32_t b_xfull = b_afull + 8 * kOpStages;            // [kOpStages]
+    const uint32_t b_consumed = b_xfull + 8 * kOpStages;         // [kOpStages]  MMA done with A/X stage
+    const uint32_t b_accfull = b_consumed + 8 * kOpStages;       // [2]
+    const uint32_t b_accempty = b_accfull + 16;                  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kRawStages + 3 * kOpStages + 4);
+
+    __shared__ int s_abort;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int i = 0; i < kRawStages; i++) { mbar_init(b_rawfull + 8 * i, 1); mbar_init(b_rawempty + 8 * i, kDecodeWarps); }
+        for (int i = 0; i < kOpStages; i++) {
+            mbar_init(b_afull + 8 * i, kDecodeWarps); mbar_init(b_xfull + 8 * i, 1); mbar_init(b_consumed + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; i++) { mbar_init(b_accfull + 8 * i, 1); mbar_init(b_accempty + 8 * i, 4); }
+        mbar_fence_init();
+    }
+    if (warp == 1) { tmem_alloc(smem_addr(tmem_slot), P.tmem_cols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    grid_launch_dependents();
+
+    const int KB = P.KB;
+    const Range rg = cta_range((long long)P.n_mtiles * P.n_ntiles * KB, gridDim.x, blockIdx.x);
+    const int tile0 = rg.lo / KB, kb0 = rg.lo - tile0 * KB;     // the only divisions of the schedule
+    const bool two_acc = 2 * BN <= (int)P.tmem_cols;             // accumulators are double buffered
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            grid_dependency_wait();                              // activations come from the predecessor
+            int sr = 0, so = 0, tile = tile0, kb = kb0;
+            int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+            uint32_t wr = 0, wo = 0;
+            for (int it = rg.lo; it < rg.hi; it++) {
+                if (wr > 0) mbar_wait(b_rawempty + 8 * sr, (wr - 1) & 1, P.status, 0x10u, &s_abort);
+                mbar_arrive_expect_tx(b_rawfull + 8 * sr, kRawBytes);
+                const uint32_t rdst = smem_addr(raw + sr * kRawBytes);
+                tma_load_2d(rdst, &map_sm, kb * kTK, mt * kTM, b_rawfull + 8 * sr);
+                tma_load_2d(rdst + kTM * kTK, &map_gr, kb * (kTK / 2), mt * kTM, b_rawfull + 8 * sr);
+                if (wo > 0) mbar_wait(b_consumed + 8 * so, (wo - 1) & 1, P.status, 0x20u, &s_abort);
+                mbar_arrive_expect_tx(b_xfull + 8 * so, xbytes);
+                tma_load_2d(smem_addr(Xbuf + (size_t)so * xbytes), &map_x, kb * kTK, nt * BN, b_xfull + 8 * so);
+                if (++sr == kRawStages) { sr = 0; wr++; }
+                if (++so == kOpStages) { so = 0; wo++; }
+                if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mt++; } }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ----------------------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
+            int so = 0, nacc = 0, it = rg.lo, tile_end = (tile0 + 1) * KB;
+            uint32_t wo = 0;
+            while (it < rg.hi) {
+                const int seg_end = tile_end < rg.hi ? tile_end : rg.hi;
+                const int buf = two_acc ? (nacc & 1) : 0;
+                const int uses = two_acc ? (nacc >> 1) : nacc;    // earlier uses of this accumulator
+                if (uses > 0) mbar_wait(b_accempty + 8 * buf, (uses - 1) & 1, P.status, 0x40u, &s_abort);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                uint32_t accumulate = 0;
+                for (; it < seg_end; it++) {
+                    mbar_wait(b_afull + 8 * so, wo & 1, P.status, 0x80u, &s_abort);
+                    mbar_wait(b_xfull + 8 * so, wo & 1, P.status, 0x100u, &s_abort);
+                    tc_fence_after();
+                    const uint64_t ad = smem_desc_sw128(smem_addr(Abuf + so * kABytes));
+                    const uint64_t bd = smem_desc_sw128(smem_addr(Xbuf + (size_t)so * xbytes));
+#pragma unroll
+                    for (int k = 0; k < kTK / 16; k++) {
+                        umma_bf16(d_tmem, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc, accumulate);
+                        accumulate = 1;
+                    }
+                    umma_commit(b_consumed + 8 * so);            // frees the A and X stage when these MMAs finish
+                    if (++so == kOpStages) { so = 0; wo++; }
+                }
+                umma_commit(b_accfull + 8 * buf);                // accumulator of this tile segment is complete
+                nacc++;
+                tile_end += KB;
+            }
+        }
+    } else if (warp >= kFirstDecodeWarp && warp < kFirstEpiWarp) {
+        // ------------------------------ decode --------------------------------
+        const int item = threadIdx.x - kFirstDecodeWarp * 32;     // 0..511 = row*4 + chunk
+        const int r = item >> 2, c = item & 3, sw = r & 7;
+        const uint32_t off_lo = r * 128 + (((2 * c) ^ sw) << 4), off_hi = r * 128 + (((2 * c + 1) ^ sw) << 4);
+        int sr = 0, so = 0, tile = tile0, kb = kb0;
+        int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+        uint32_t wr = 0, wo = 0;
+        for (int it = rg.lo; it < rg.hi; it++) {
+            mbar_wait(b_rawfull + 8 * sr, wr & 1, P.status, 0x200u, &s_abort);
+            if (wo > 0) mbar_wait(b_consumed + 8 * so, (wo - 1) & 1, P.status, 0x400u, &s_abort);
+            const uint8_t* rawp = raw + sr * kRawBytes;
+            uint8_t* Ap = Abuf + so * kABytes;
+            if (P.neg_base) decode_item<1>(rawp, Ap, item, off_lo, off_hi, P.base2, P, mt * kTM, kb * kTK);
+            else decode_item<0>(rawp, Ap, item, off_lo, off_hi, P.base2, P, mt * kTM, kb * kTK);
+            fence_async_smem();                                   // generic-proxy writes -> visible to the MMA
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(b_afull + 8 * so); mbar_arrive(b_rawempty + 8 * sr); }
+            if (++sr == kRawStages) { sr = 0; wr++; }
+            if (++so == kOpStages) { so = 0; wo++; }
+            if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mt++; } }
+        }
+    } else if (warp >= kFirstEpiWarp) {
+        // ------------------------------ epilogue ------------------------------
+        grid_dependency_wait();                                   // the output buffer may still be in use
+        const int q = warp & 3;                                   // TMEM lane quarter this warp may read
+        const int mrow = q * 32 + lane;                           // accumulator row held by this thread
+        int nacc = 0, it = rg.lo, tile = tile0;
+        while (it < rg.hi) {
+            const int tile_lo = tile * KB, tile_end = tile_lo + KB;
+            const int seg_end = tile_end < rg.hi ? tile_end : rg.hi;
+            const bool whole = it == tile_lo && seg_end == tile_end;
+            const int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+            const int buf = two_acc ? (nacc & 1) : 0;
+            const int uses = two_acc ? (nacc >> 1) : nacc;
+            mbar_wait(b_accfull + 8 * buf, uses & 1, P.status, 0x800u, &s_abort);
+            tc_fence_after();
+            const int m = mt * kTM + mrow;
+            const int b0 = nt * BN;
+            // A segment that covers only part of its tile's K range goes to the
+            // workspace (slot 0: the tile this CTA's range starts in, slot 1: the
+            // tile it ends in) and is summed by gemm_reduce_kernel.
+            float* wsp = P.ws + ((size_t)blockIdx.x * 2 + (it == rg.lo ? 0 : 1)) * (size_t)BN * kTM;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+                tmem_ld_wait();
+                if (whole) {
+                    if (m < P.M) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (b0 + c0 + j < P.B) P.out[(size_t)(b0 + c0 + j) * P.out_stride + m] = __uint_as_float(v[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (c0 + j < BN) wsp[(size_t)(c0 + j) * kTM + mrow] = __uint_as_float(v[j]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_accempty + 8 * buf);     // accumulator may be overwritten
+            nacc++;
+            it = seg_end;
+            tile++;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
+}
+
+// Sums the partial accumulators of every tile whose K range was shared by
+// several CTAs, in CTA order (deterministic), and stores the result.  One CTA
+// per (tile, 32-sequence slab); tiles owned by a single CTA were stored by the
+// GEMM kernel itself and exit at once.
+__global__ void __launch_bounds__(256)
+gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int tile = blockIdx.x, KB = P.KB, BN = P.BN;
+    const long long T = (long long)P.n_mtiles * P.n_ntiles * KB;
+    const int tile_lo = tile * KB, tile_end = tile_lo + KB;
+    int c_first = (int)(((long long)tile_lo * G) / T);
+    while (c_first > 0 && cta_range(T, G, c_first).lo > tile_lo) c_first--;
+    while (cta_range(T, G, c_first).hi <= tile_lo) c_first++;
+    int c_last = c_first;
+    while (c_last + 1 < G && cta_range(T, G, c_last + 1).lo < tile_end) c_last++;
+    if (c_first == c_last) return;
+    const int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+    const int m4 = (threadIdx.x & 31) * 4;                       // four consecutive rows per thread
+    const int b0 = nt * BN;
+    for (int j = blockIdx.y * 32 + (threadIdx.x >> 5); j < blockIdx.y * 32 + 32 && j < BN; j += 8) {
+        if (b0 + j >= P.B) break;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = c_first; c <= c_last; c++) {
+            const int slot = cta_range(T, G, c).lo >= tile_lo ? 0 : 1;
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                P.ws + ((size_t)c * 2 + slot) * (size_t)BN * kTM + (size_t)j * kTM + m4));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int m = mt * kTM + m4;
+        float* dst = P.out + (size_t)(b0 + j) * P.out_stride + m;
+        if (m + 3 < P.M && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            *reinterpret_cast<float4*>(dst) = acc;
+        } else {
+            if (m < P.M) dst[0] = acc.x;
+            if (m + 1 < P.M) dst[1] = acc.y;
+            if (m + 2 < P.M) dst[2] = acc.z;
+            if (m + 3 < P.M) dst[3] = acc.w;
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+                     uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t es[2] = {1, 1};
+    return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Per-device workspace for partial accumulators (grow-only, allocated on first
+// use or when a larger one is needed).
+struct Scratch { float* ws = nullptr; size_t ws_bytes = 0; };
+static Scratch g_scratch[64];
+static std::mutex g_scratch_mu;
+
+static int get_scratch(size_t ws_bytes, Scratch& out, const char* who)
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = (dev < 0 || dev >= 64) ? 0 : dev;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    Scratch& s = g_scratch[dev];
+    if (s.ws_bytes < ws_bytes) {
+        cudaDeviceSynchronize();
+        if (s.ws) cudaFree(s.ws);
+        s.ws = nullptr; s.ws_bytes = 0;
+        int rc = check_cuda(cudaMalloc(&s.ws, ws_bytes), who);
+        if (rc) return rc;
+        s.ws_bytes = ws_bytes;
+    }
+    out = s;
+    return S12_OK;
+}
+
+int gemm_tc_supported(const S12Tensor* w, int act_stride, int out_stride, int B)
+{
+    (void)out_stride;
+    if (B <= 16 || w->M < 1 || w->K < kTK) return 0;
+    if (w->K % 32 != 0 || act_stride % 8 != 0) return 0;
+    if (w->base_exp < -1 || w->base_exp > 240) return 0;
+    if (reinterpret_cast<uintptr_t>(w->sm) % 16 || reinterpret_cast<uintptr_t>(w->gr) % 16) return 0;
+    return encode_fn() != nullptr;
+}
+
+int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
+                   int B, void* stream, const char* who)
+{
+    if (reinterpret_cast<uintptr_t>(act) % 16) return fail(S12_ERR_UNSUPPORTED, "%s: activations must be 16-byte aligned", who);
+    GemmParams P = {};
+    const bool csr = w->row_off && w->cols && w->correct;
+    P.row_off = csr ? w->row_off : nullptr; P.cols = w->cols; P.correct = w->correct;
+    P.out = (float*)out; P.M = w->M; P.K = w->K; P.B = B; P.out_stride = out_stride;
+    P.BN = B >= 256 ? 256 : ((B + 15) / 16) * 16;
+    if (P.BN < 32) P.BN = 32;
+    P.n_mtiles = (w->M + kTM - 1) / kTM;
+    P.n_ntiles = (B + P.BN - 1) / P.BN;
+    P.KB = (w->K + kTK - 1) / kTK;
+    P.base2 = make_base2(w->base_exp);
+    P.neg_base = w->base_exp < 0;
+    uint32_t cols = 32;
+    while (cols < (uint32_t)(2 * P.BN) && cols < 512) cols <<= 1;
+    P.tmem_cols = cols;
+    P.status = device_status_word();
+
+    CUtensorMap msm, mgr, mx;
+    if (!make_map(&msm, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->sm, (uint64_t)w->K, (uint64_t)w->M, (uint64_t)w->K,
+                  kTK, kTM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_map(&mgr, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->gr, (uint64_t)w->K / 2, (uint64_t)w->M, (uint64_t)w->K / 2,
+                  kTK / 2, kTM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)w->K, (uint64_t)B, (uint64_t)act_stride * 2,
+                  kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
+
+    const long long T = (long long)P.n_mtiles * P.n_ntiles * P.KB;
+    if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: problem too large for the tile schedule", who);
+    const int sms = sm_count();
+    int grid = T < sms ? (int)T : sms;
+    // do not cut tiles finer than ~8 K blocks per CTA: the fix-up traffic would dominate
+    const long long min_iters = 8;
+    if (T / grid < min_iters) grid = (int)((T + min_iters - 1) / min_iters);
+    if (grid < 1) grid = 1;
+    Scratch sc;
+    int rc = get_scratch((size_t)sms * 2 * 256 * kTM * sizeof(float), sc, who);   // sized for the largest launch
+    if (rc) return rc;
+    P.ws = sc.ws;
+    // does any tile have its K range shared between CTAs?
+    bool partial = false;
+    for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(T, grid, c).hi % P.KB != 0;
+
+    const size_t smem = (size_t)kRawStages * kRawBytes + (size_t)kOpStages * kABytes + (size_t)kOpStages * P.BN * 128 +
+                        8 * (2 * kRawStages + 3 * kOpStages + 4) + 16 + 1024;
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = (dev < 0 || dev >= 64) ? 0 : dev;
+    if (!attr_set[dev]) {
+        cudaFuncAttributes fa;
+        rc = check_cuda(cudaFuncGetAttributes(&fa, gemm_tc_kernel), who);
+        if (rc) return rc;
+        rc = check_cuda(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             227 * 1024 - (int)fa.sharedSizeBytes), who);
+        if (rc) return rc;
+        attr_set[dev] = true;
+    }
+    rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, msm, mgr, mx, P);
+    if (rc || !partial) return rc;
+    return launch(gemm_reduce_kernel, dim3(P.n_mtiles * P.n_ntiles, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
+}
+
 }  // namespace s12

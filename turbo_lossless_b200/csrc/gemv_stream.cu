@@ -121,7 +121,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
     const uint32_t bar_rowdone = bar_empty + 8 * kMaxDepth;      // [kRedSlots]
     const uint32_t bar_redfree = bar_rowdone + 8 * kRedSlots;    // [kRedSlots]
 
+    __shared__ int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) s_abort = 0;
     if (warp == 0) S12_STAMP(0);
     if (threadIdx.x < kMaxDepth) {
         mbar_init(bar_full + 8 * threadIdx.x, 1);
@@ -157,7 +159,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         uint32_t wrap = 0;                                   // times the ring index wrapped
         BlockRef br = locate_block(P, blk);
         for (int i = 0; i < ntiles; i++) {
-            if (i >= depth) mbar_wait(bar_empty + 8 * s, (wrap - 1) & 1, P.status, 1u);
+            if (i >= depth) mbar_wait(bar_empty + 8 * s, (wrap - 1) & 1, P.status, 1u, &s_abort);
             const StreamTensor& T = P.t[br.ti];
             const int col0 = kt * tile_cols;
             const int ncols = K - col0 > tile_cols ? tile_cols : K - col0;
@@ -238,7 +240,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         uint32_t wrap = grp / depth;
         for (int i = grp; i < ntiles; i += kGroups) {
             if (jb != jb_loaded) { base2 = P.t[locate_block(P, b0 + jb).ti].base2; jb_loaded = jb; }
-            mbar_wait(bar_full + 8 * s, wrap & 1, P.status, 2u);
+            mbar_wait(bar_full + 8 * s, wrap & 1, P.status, 2u, &s_abort);
             if (warp == 0 && i == 0) S12_STAMP(3);
             const uint8_t* st = ring + (size_t)s * kStageBytes;
             const uint4 af = *reinterpret_cast<const uint4*>(st + offA + first);
@@ -279,7 +281,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             if (jb_next != jb || i + kGroups >= ntiles) {
                 // this warp's share of row block jb is complete: publish its 16 segment sums
                 const int slot = jb % kRedSlots;
-                if (jb >= kRedSlots) mbar_wait(bar_redfree + 8 * slot, ((jb / kRedSlots) - 1) & 1, P.status, 4u);
+                if (jb >= kRedSlots) mbar_wait(bar_redfree + 8 * slot, ((jb / kRedSlots) - 1) & 1, P.status, 4u, &s_abort);
                 float* r = red + (slot * kConsumers + warp) * 16;
                 const float c0 = acc[0][0] + acc[1][0], c1 = acc[0][1] + acc[1][1];
                 const float c2 = acc[0][2] + acc[1][2], c3 = acc[0][3] + acc[1][3];
@@ -327,7 +329,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         const int jfirst = grp * gb;
         const int jlast = (jfirst + gb < nblocks ? jfirst + gb : nblocks) - 1;
         for (int j = jfirst; j <= jlast; j++)
-            mbar_wait(bar_rowdone + 8 * (j % kRedSlots), (j / kRedSlots) & 1, P.status, 8u);
+            mbar_wait(bar_rowdone + 8 * (j % kRedSlots), (j / kRedSlots) & 1, P.status, 8u, &s_abort);
         if (lane < 16 && have) {
             const float* r = red + (jb % kRedSlots) * kConsumers * 16;
             float v = corr;
@@ -392,11 +394,14 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
 
     const size_t fixed = (size_t)P.tpr * Q * kXChunkUnits * 16 + kRedSlots * kConsumers * 16 * sizeof(float) +
                          8 * (2 * kMaxDepth + 2 * kRedSlots);
-    static int max_smem = 0;
+    static int max_smem = 0;                 // dynamic shared memory a CTA of this kernel may ask for
     if (!max_smem) {
-        int dev = 0;
+        int dev = 0, optin = 0;
         cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, gemv_stream_kernel<0>) != cudaSuccess) fa.sharedSizeBytes = 1024;
+        max_smem = optin - (int)fa.sharedSizeBytes - 64;
     }
     int depth = (int)(((size_t)max_smem - fixed) / kStageBytes);
     if ((size_t)max_smem < fixed + 2 * (size_t)kStageBytes) return 0;   // K too large for this layout
