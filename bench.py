@@ -159,6 +159,12 @@ def model_tensors(model):
     return out
 
 
+def _log(msg):
+    if os.environ.get("S12_BENCH_VERBOSE"):
+        sys.stderr.write(f"[bench r{os.environ.get('RANK', '0')} {time.strftime('%H:%M:%S')}] {msg}\n")
+        sys.stderr.flush()
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -174,7 +180,9 @@ def run_ours(args):
     layers = args.layers or cfg["layers"]
     B, H, V = cfg["batch"], cfg["hidden"], cfg["vocab"]
     eng = Split12Engine()
+    _log("process group up; building model")
     model = build_model(cfg, rank, world, layers, torch, CompressedWeight)
+    _log("model packed")
     tensors = model_tensors(model)
     comp_bytes = sum(t.compressed_bytes for t in tensors)             # this rank
     weights = sum(t.M * t.K for t in tensors)
@@ -215,22 +223,41 @@ def run_ours(args):
                 eng.gemm(w, x, o, x.shape[1], o.shape[1], B)
                 launches[0] += 1
 
+    # The step as a list of segments: ("k", fn) = our launches only (capturable as one CUDA graph),
+    # ("ar", tensor) = the all-reduce after a row-parallel projection.  NCCL collectives are kept
+    # out of graph capture (capturing them hung on this pool), so with N > 1 a step replays one
+    # small graph per segment and calls all_reduce between them.
+    segments = []
+
+    def add_k(fn):
+        if segments and segments[-1][0] == "k":
+            prev = segments[-1][1]
+            segments[-1] = ("k", lambda prev=prev, fn=fn: (prev(), fn()))
+        else:
+            segments.append(("k", fn))
+
+    for L in model["layers"]:
+        if "wk" in L:
+            add_k(lambda L=L: proj([L["wq"], L["wk"], L["wv"]], x_hidden, [o_q, o_k, o_v]))
+            add_k(lambda L=L: proj([L["wo"]], x_attn, [o_o]))
+            if world > 1:
+                segments.append(("ar", o_o))
+        else:
+            add_k(lambda L=L: proj([L["wq"]], x_hidden, [o_q]))
+        if "w_gate" in L:
+            add_k(lambda L=L: proj([L["w_gate"], L["w_up"]], x_hidden, [o_g, o_u]))
+            add_k(lambda L=L: proj([L["w_down"]], x_ffn, [o_d]))
+            if world > 1:
+                segments.append(("ar", o_d))
+    if model["lm_head"] is not None:
+        add_k(lambda: proj([model["lm_head"]], x_hidden, [logits]))
+
     def step():
-        for L in model["layers"]:
-            if "wk" in L:
-                proj([L["wq"], L["wk"], L["wv"]], x_hidden, [o_q, o_k, o_v])
-                proj([L["wo"]], x_attn, [o_o])
-                if world > 1:
-                    dist.all_reduce(o_o)
+        for kind, item in segments:
+            if kind == "k":
+                item()
             else:
-                proj([L["wq"]], x_hidden, [o_q])
-            if "w_gate" in L:
-                proj([L["w_gate"], L["w_up"]], x_hidden, [o_g, o_u])
-                proj([L["w_down"]], x_ffn, [o_d])
-                if world > 1:
-                    dist.all_reduce(o_d)
-        if model["lm_head"] is not None:
-            proj([model["lm_head"]], x_hidden, [logits])
+                dist.all_reduce(item)
 
     eng.set_dependent_launch(not args.no_pdl)
     stream = torch.cuda.Stream()
@@ -238,17 +265,34 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         step()                                   # also loads every kernel before capture
         torch.cuda.synchronize()
+        _log("first eager step done")
         launches_per_step = launches[0]
         if not args.no_graph:
             try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    step()
+                graphs = []
+                for kind, item in segments:
+                    if kind != "k":
+                        graphs.append((kind, item))
+                        continue
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        item()
+                    graphs.append(("g", g))
+                graph = graphs
             except Exception as e:               # eager launches still measure the same work
                 sys.stderr.write(f"[bench] graph capture failed ({e}); launching eagerly\n")
                 graph = None
                 torch.cuda.synchronize()
-        run = graph.replay if graph is not None else step
+
+        def replay():
+            for kind, item in graph:
+                if kind == "g":
+                    item.replay()
+                else:
+                    dist.all_reduce(item)
+
+        run = replay if graph is not None else step
+        _log("graph(s) captured: %d segments" % len(graph) if graph is not None else "eager mode")
 
         def barrier():
             if world > 1:
@@ -269,6 +313,7 @@ def run_ours(args):
         barrier()
         ms = e0.elapsed_time(e1)
         clocks = sampler.stop() if rank == 0 else None
+        _log(f"timed region done: {ms / args.steps:.3f} ms/step")
 
         # end to end: pinned host activations in, logits back to the host, every step
         for _ in range(2):
