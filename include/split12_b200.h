@@ -188,6 +188,25 @@ int s12_gemv_batched_async(const S12Tensor* w, const void* act, int act_stride,
 int s12_gemm_async(const S12Tensor* w, const void* act, int act_stride,
                    void* out, int out_stride, int B, void* stream);
 
+/* Same result as s12_gemm_async for 17 <= B <= 256, for callers that must not
+ * allocate device memory after start-up (a server that gave the whole GPU to
+ * its own memory pool, a latency-critical loop that cannot afford cudaMalloc's
+ * locks and implicit synchronisation).  No counterpart in the reference.  The
+ * stream-K partial sums go to a fixed 8 MiB array that is part of the library
+ * image on every GPU that loads it, instead of a cudaMalloc'd workspace; the
+ * number of CTAs is reduced until their partials fit, so large problems run
+ * slower than through s12_gemm_async.  The call never calls cudaMalloc, cudaFree
+ * or any allocating library routine.  Limits: B > 256 is refused with
+ * S12_ERR_TOO_LARGE; B <= 16, K < 64, K % 32 != 0 or unaligned pointers with
+ * S12_ERR_UNSUPPORTED.  The first call on each device looks up the array's
+ * device address (cudaGetSymbolAddress) and sets a kernel attribute; make that
+ * first call before any stream capture.  All calls on a device share the one
+ * array: calls whose kernels may overlap on the GPU (different streams) race
+ * on it and must be serialised by the caller.  Nothing in the array needs to
+ * start at zero: every partial is written before it is read in the same call. */
+int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int act_stride,
+                           void* out, int out_stride, int B, void* stream);
+
 /* Programmatic dependent launch for every kernel of this library on the
  * calling thread's subsequent calls: a kernel may start while its predecessor
  * in the stream drains and prefetch its (read-only) weights before waiting

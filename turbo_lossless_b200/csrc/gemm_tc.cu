@@ -522,3 +522,127 @@ int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* ou
 }
 
 }  // namespace s12
+
+// ----------------------------------------------------------------------------
+// Allocation-free variant of the batched GEMM
+// ----------------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory once they are
+// running: an inference server that has handed all of the GPU's memory to its
+// own pool at start-up, a real-time loop that must not take the allocator's
+// locks or its implicit synchronisation, or code that runs under a memory
+// budget checked at load time.  For them the partial-accumulator workspace of
+// the stream-K schedule lives in a fixed array inside the library image instead
+// of being obtained with cudaMalloc.  The array costs kNoAllocWsBytes on every
+// GPU that loads the library, so it is kept small and the CTA count of a launch
+// is reduced until its partials fit (fewer CTAs: slower, same result).
+namespace s12 {
+
+constexpr size_t kNoAllocWsBytes = 8u << 20;                       // 8 MiB per GPU
+constexpr size_t kNoAllocWsFloats = kNoAllocWsBytes / sizeof(float);
+constexpr int kNoAllocMaxB = 256;                                  // one tile of sequences
+
+static __device__ __align__(256) float g_noalloc_ws[kNoAllocWsFloats];
+static __device__ unsigned int g_noalloc_status;
+
+struct NoAllocState { float* ws; unsigned int* status; bool ready; };
+static NoAllocState g_noalloc[64];
+static std::mutex g_noalloc_mu;
+
+// Device addresses of the two symbols for the current device.  In host code
+// the array names are only handles; the kernel needs what cudaGetSymbolAddress
+// returns for the device that is current now.
+static int noalloc_setup(NoAllocState& out, const char* who)
+{
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), who);
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return fail(S12_ERR_UNSUPPORTED, "%s: device ordinal %d not supported", who, dev);
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocState& st = g_noalloc[dev];
+    if (!st.ready) {
+        float* ws = nullptr;
+        unsigned int* status = nullptr;
+        rc = check_cuda(cudaGetSymbolAddress((void**)&ws, g_noalloc_ws), who);
+        if (rc) return rc;
+        rc = check_cuda(cudaGetSymbolAddress((void**)&status, g_noalloc_status), who);
+        if (rc) return rc;
+        cudaFuncAttributes fa;
+        rc = check_cuda(cudaFuncGetAttributes(&fa, gemm_tc_kernel), who);
+        if (rc) return rc;
+        rc = check_cuda(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             227 * 1024 - (int)fa.sharedSizeBytes), who);
+        if (rc) return rc;
+        st.ws = ws; st.status = status; st.ready = true;
+    }
+    out = st;
+    return S12_OK;
+}
+
+}  // namespace s12
+
+extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int act_stride,
+                                      void* out, int out_stride, int B, void* stream)
+{
+    using namespace s12;
+    const char* who = "s12_gemm_noalloc_async";
+    if (!w || !act || !out) return fail(S12_ERR_BAD_ARG, "%s: null argument", who);
+    if (B > kNoAllocMaxB)
+        return fail(S12_ERR_TOO_LARGE, "%s: B=%d exceeds the maximum of %d sequences per call", who, B, kNoAllocMaxB);
+    if (B <= 16) return fail(S12_ERR_UNSUPPORTED, "%s: B=%d; this entry point covers 17..%d (smaller batches need no scratch: use s12_gemv_batched_async)", who, B, kNoAllocMaxB);
+    if (w->M < 1 || w->K < kTK || (w->K % 32) != 0 || (act_stride % 8) != 0 || act_stride < w->K || out_stride < w->M)
+        return fail(S12_ERR_UNSUPPORTED, "%s: needs M>=1, K>=64, K%%32==0, act_stride%%8==0, act_stride>=K, out_stride>=M", who);
+    if (w->base_exp < -1 || w->base_exp > 240) return fail(S12_ERR_BAD_ARG, "%s: base_exp=%d", who, w->base_exp);
+    if (!w->sm || !w->gr || reinterpret_cast<uintptr_t>(w->sm) % 16 || reinterpret_cast<uintptr_t>(w->gr) % 16 ||
+        reinterpret_cast<uintptr_t>(act) % 16)
+        return fail(S12_ERR_UNSUPPORTED, "%s: sm, gr and activations must be 16-byte aligned", who);
+    if (!encode_fn()) return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled unavailable", who);
+
+    NoAllocState st;
+    int rc = noalloc_setup(st, who);
+    if (rc) return rc;
+
+    GemmParams P = {};
+    const bool csr = w->row_off && w->cols && w->correct;
+    P.row_off = csr ? w->row_off : nullptr; P.cols = w->cols; P.correct = w->correct;
+    P.out = (float*)out; P.M = w->M; P.K = w->K; P.B = B; P.out_stride = out_stride;
+    P.BN = ((B + 15) / 16) * 16;
+    if (P.BN < 32) P.BN = 32;
+    P.n_mtiles = (w->M + kTM - 1) / kTM;
+    P.n_ntiles = 1;
+    P.KB = (w->K + kTK - 1) / kTK;
+    P.base2 = make_base2(w->base_exp);
+    P.neg_base = w->base_exp < 0;
+    uint32_t cols = 32;
+    while (cols < (uint32_t)(2 * P.BN) && cols < 512) cols <<= 1;
+    P.tmem_cols = cols;
+    P.status = st.status;
+    P.ws = st.ws;
+
+    const long long T = (long long)P.n_mtiles * P.KB;
+    if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: M*K exceeds the tile schedule's range", who);
+    CUtensorMap msm, mgr, mx;
+    if (!make_map(&msm, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->sm, (uint64_t)w->K, (uint64_t)w->M, (uint64_t)w->K,
+                  kTK, kTM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_map(&mgr, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->gr, (uint64_t)w->K / 2, (uint64_t)w->M, (uint64_t)w->K / 2,
+                  kTK / 2, kTM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)w->K, (uint64_t)B, (uint64_t)act_stride * 2,
+                  kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
+
+    // CTAs: as the regular path, then capped so that two partial tiles per CTA fit the fixed scratch
+    const int sms = sm_count();
+    int grid = T < sms ? (int)T : sms;
+    if (T / grid < 8) grid = (int)((T + 7) / 8);
+    const size_t per_cta = (size_t)2 * P.BN * kTM;
+    const int fit = (int)(kNoAllocWsFloats / per_cta);
+    if (grid > fit) grid = fit;
+    if (grid < 1) grid = 1;
+    bool partial = false;
+    for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(T, grid, c).hi % P.KB != 0;
+
+    const size_t smem = (size_t)kRawStages * kRawBytes + (size_t)kOpStages * kABytes + (size_t)kOpStages * P.BN * 128 +
+                        8 * (2 * kRawStages + 3 * kOpStages + 4) + 16 + 1024;
+    rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, msm, mgr, mx, P);
+    if (rc || !partial) return rc;
+    return launch(gemm_reduce_kernel, dim3(P.n_mtiles, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
+}

@@ -283,6 +283,13 @@ class Split12Engine:
         check(self.lib.s12_gemm_async(C.byref(t), _ptr(bf16_in), act_stride, _ptr(out), out_stride, bs,
                                       _stream(stream)), "s12_gemm_async")
 
+    def gemm_noalloc(self, w: CompressedWeight, bf16_in: torch.Tensor, out: torch.Tensor, act_stride: int,
+                     out_stride: int, bs: int, stream=None, exact: bool = True) -> None:
+        """s12_gemm_async for callers that may not allocate: scratch is a fixed array in the library."""
+        t = w.tensor(with_csr=exact)
+        check(self.lib.s12_gemm_noalloc_async(C.byref(t), _ptr(bf16_in), act_stride, _ptr(out), out_stride, bs,
+                                              _stream(stream)), "s12_gemm_noalloc_async")
+
     def decompress(self, w: CompressedWeight, out: Optional[torch.Tensor] = None, stream=None,
                    exact: bool = True) -> torch.Tensor:
         """Lossless bf16 [M,K] (int16 storage); with exact=False escapes keep the "wrong" value."""
