@@ -45,12 +45,10 @@ namespace s12 {
 constexpr int kSegCols      = 1024;
 constexpr int kGrBase       = 16 * kSegCols;                             // gr part of a stage
 constexpr int kStageBytes   = kGrBase + 16 * (kSegCols / 2);             // 24576: dense image of the tile
-constexpr int kGroups       = 2;        // consumer groups, working on alternate tiles
-constexpr int kGroupWarps   = 8;        // warps per group: 128 columns of every segment each
-constexpr int kConsumers    = kGroups * kGroupWarps;
+constexpr int kGroupWarps   = 8;        // warps per consumer group: 128 columns of every segment each
 constexpr int kXChunkUnits  = kSegCols / 8 + 4;   // 16-byte units per activation chunk incl. 64 B stagger
 constexpr int kEpiWarps     = 2;
-constexpr int kStreamThreads = (kConsumers + 1 + kEpiWarps) * 32;
+constexpr int stream_threads(int groups) { return (groups * kGroupWarps + 1 + kEpiWarps) * 32; }
 constexpr int kRedSlots     = 24;       // row blocks whose partial sums may be pending
 constexpr int kMaxDepth     = 8;
 
@@ -105,10 +103,16 @@ __device__ __forceinline__ BlockRef locate_block(const StreamParams& P, int blk)
     return BlockRef{ti, (blk - first) * P.R};
 }
 
-template <int kMode>
-__global__ void __launch_bounds__(kStreamThreads, 1)
+// kGroups consumer groups work on alternate tiles.  Two groups: one CTA per SM
+// with the whole shared memory as ring.  One group: a CTA needs under half of
+// an SM, so two CTAs share it -- of one launch, or, under programmatic
+// dependent launch, the last CTAs of one launch and the first of the next,
+// whose producer then fills its ring while the predecessor drains.
+template <int kMode, int kGroups>
+__global__ void __launch_bounds__(stream_threads(kGroups), kGroups == 1 ? 2 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams P)
 {
+    constexpr int kConsumers = kGroups * kGroupWarps;
     extern __shared__ __align__(128) uint8_t smem[];
     const int depth = P.depth;
     const int xunits = P.tpr * P.Q * kXChunkUnits;               // 16-byte units of permuted x
@@ -392,36 +396,54 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     P.total_blocks = blocks;
     P.status = device_status_word();
 
-    const size_t fixed = (size_t)P.tpr * Q * kXChunkUnits * 16 + kRedSlots * kConsumers * 16 * sizeof(float) +
+    // Shape of the launch: consumer groups per CTA and CTAs per SM (tuning knobs
+    // S12_GEMV_GROUPS / S12_GEMV_CTAS).  Default: one group, two CTAs per SM.
+    int groups = env_int2("S12_GEMV_GROUPS", 1);
+    groups = groups == 2 ? 2 : 1;
+    int ctas = groups == 2 ? 1 : env_int2("S12_GEMV_CTAS", 2);
+    ctas = ctas == 1 ? 1 : 2;
+    const int consumers = groups * kGroupWarps;
+    const size_t fixed = (size_t)P.tpr * Q * kXChunkUnits * 16 + (size_t)kRedSlots * consumers * 16 * sizeof(float) +
                          8 * (2 * kMaxDepth + 2 * kRedSlots);
-    static int max_smem = 0;                 // dynamic shared memory a CTA of this kernel may ask for
-    if (!max_smem) {
-        int dev = 0, optin = 0;
+    static int optin = 0, static_smem = 0;
+    if (!optin) {
+        int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         cudaFuncAttributes fa;
-        if (cudaFuncGetAttributes(&fa, gemv_stream_kernel<0>) != cudaSuccess) fa.sharedSizeBytes = 1024;
-        max_smem = optin - (int)fa.sharedSizeBytes - 64;
+        static_smem = cudaFuncGetAttributes(&fa, gemv_stream_kernel<0, 1>) == cudaSuccess ? (int)fa.sharedSizeBytes : 1024;
     }
-    int depth = (int)(((size_t)max_smem - fixed) / kStageBytes);
-    if ((size_t)max_smem < fixed + 2 * (size_t)kStageBytes) return 0;   // K too large for this layout
+    // dynamic shared memory one CTA may use: everything, or what lets two CTAs (1 KB reserved each) share an SM
+    const int per_cta = (ctas == 2 ? (optin + 1024) / 2 - 1024 : optin) - static_smem - 64;
+    if ((size_t)per_cta < fixed + 2 * (size_t)kStageBytes) {
+        if (ctas == 2) ctas = 1;            // long rows: the activation vector needs the room
+        else return 0;
+    }
+    const int budget = (ctas == 2 ? (optin + 1024) / 2 - 1024 : optin) - static_smem - 64;
+    if ((size_t)budget < fixed + 2 * (size_t)kStageBytes) return 0;   // K too large for this layout
+    int depth = (int)(((size_t)budget - fixed) / kStageBytes);
     if (depth > kMaxDepth) depth = kMaxDepth;
     if (force_depth >= 2 && force_depth < depth) depth = force_depth;
     P.depth = depth;
     const size_t smem = fixed + (size_t)depth * kStageBytes;
 
-    auto kern = mode == 0 ? gemv_stream_kernel<0> : mode == 1 ? gemv_stream_kernel<1> : gemv_stream_kernel<2>;
-    static bool attr_set[64][3];
+    typedef void (*Kern)(const StreamParams);
+    static const Kern table[2][3] = {
+        {gemv_stream_kernel<0, 1>, gemv_stream_kernel<1, 1>, gemv_stream_kernel<2, 1>},
+        {gemv_stream_kernel<0, 2>, gemv_stream_kernel<1, 2>, gemv_stream_kernel<2, 2>}};
+    Kern kern = table[groups - 1][mode];
+    static bool attr_set[64][2][3];
     int dev = 0;
     cudaGetDevice(&dev);
     dev = (dev < 0 || dev >= 64) ? 0 : dev;
-    if (!attr_set[dev][mode]) {
-        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem), who);
+    if (!attr_set[dev][groups - 1][mode]) {
+        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - static_smem - 64), who);
         if (rc) { *rc_out = rc; return -1; }
-        attr_set[dev][mode] = true;
+        attr_set[dev][groups - 1][mode] = true;
     }
-    const int grid = blocks < sms ? blocks : sms;
-    *rc_out = launch(kern, dim3(grid), dim3(kStreamThreads), smem, stream, who, P);
+    const int slots = sms * ctas;
+    const int grid = blocks < slots ? blocks : slots;
+    *rc_out = launch(kern, dim3(grid), dim3(stream_threads(groups)), smem, stream, who, P);
     return *rc_out == S12_OK ? 1 : -1;
 }
 
