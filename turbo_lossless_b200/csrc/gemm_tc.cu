@@ -3,28 +3,32 @@
 //
 //   C[b, m] = sum_k W[m, k] * X[b, k]      fp32 out[b*out_stride + m]
 //
-// Roles inside one persistent CTA (one CTA per SM, 16 warps):
-//   warp 0       producer: TMA tensor-map loads of the raw packed tile
-//                (128 rows x 64 sm bytes, 128 x 32 gr bytes) and of the
-//                activation tile (BN sequences x 64 k, 128-byte swizzle)
+// Roles inside one persistent CTA (one CTA per SM, 24 warps).  A CTA tile is
+// kTileRows weight rows x BN sequences (kHalves 128-row MMA blocks sharing one
+// activation tile).
+//   warp 0       raw-tile producer: TMA tensor-map loads of the packed tile
+//                (rows x 64 sm bytes, rows x 32 gr bytes) into a deep ring;
+//                runs ahead of everything else, weights come from HBM
+//   warp 2       activation producer: TMA loads of the activation tile
+//                (BN sequences x 64 k, 128-byte swizzle) into its own ring
 //   warp 1       owns tensor memory (alloc/dealloc) and issues the MMAs from
-//                one thread: per 64-column block four tcgen05.mma
+//                one thread: per 64-column block kHalves x 4 tcgen05.mma
 //                (M=128, N=BN, K=16, bf16 x bf16 -> fp32 in TMEM)
-//   warps 4-11   decode: raw bytes -> bf16 (decode8, escapes patched from the
+//   warps 4-19   decode: raw bytes -> bf16 (decode8, escapes patched from the
 //                CSR list when the tensor brings one) written into the
-//                K-major, 128-byte-swizzled A tile the MMA descriptor expects,
+//                K-major, 128-byte-swizzled A tiles the MMA descriptor expects,
 //                then fence.proxy.async + mbarrier arrive
-//   warps 12-15  epilogue: tcgen05.ld of the finished accumulator (double
-//                buffered in TMEM, so it overlaps the next tile's main loop),
-//                coalesced fp32 stores (32 consecutive m per store)
-//   warps 2-3    idle
+//   warps 20-23  epilogue: tcgen05.ld of the finished accumulators (double
+//                buffered in TMEM when 4*BN <= 512 columns), coalesced fp32
+//                stores (32 consecutive m per store)
+//   warp 3       idle
 //
 // Work is split stream-K style: the (M tiles x N tiles x K blocks) iteration
 // space is cut into equal contiguous ranges, one per CTA, so a 4096-row
 // projection (32 tiles) still occupies all 148 SMs.  A CTA that covers only
-// part of a tile's K range writes its partial accumulator to a workspace; the
-// last contributor of a tile (an atomic counter, no waiting) adds the partials
-// in a fixed order and stores the result, so the output is deterministic.
+// part of a tile's K range writes its partial accumulator to a workspace and
+// gemm_reduce_kernel adds the partials of each such tile in CTA order, so the
+// output is deterministic.
 //
 // Escapes: with the CSR list the decoded weights are exact inside the MMA;
 // without it they keep the reference's "wrong" value (exponent base_exp), which
@@ -40,22 +44,33 @@
 
 namespace s12 {
 
-constexpr int kTM = 128;                 // weight rows per tile
+constexpr int kTM = 128;                 // rows of one MMA (tcgen05 M)
+constexpr int kHalves = 1;               // MMA row blocks per CTA tile sharing one activation tile (1 or 2)
+constexpr int kTileRows = kTM * kHalves; // weight rows per CTA tile
 constexpr int kTK = 64;                  // columns per K block
-constexpr int kRawStages = 4;
-constexpr int kOpStages = 3;             // decoded-A and activation stages
-constexpr int kRawBytes = kTM * kTK + kTM * kTK / 2;      // 12288
-constexpr int kABytes = kTM * kTK * 2;                    // 16384
+// Three independent rings.  Raw packed tiles come from HBM (about a microsecond
+// away) and are small, so that ring is deep; activation tiles come from L2;
+// decoded A tiles are produced and consumed inside the SM.
+constexpr int kRawStages = kHalves == 1 ? 5 : 3;
+constexpr int kDecodeGroups = 4;         // decode warp groups; each owns one decoded-A stage
+constexpr int kAStages = kDecodeGroups;
+constexpr int kXStages = kHalves == 1 ? 3 : 2;
+constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2 * kXStages + 4;
+constexpr int kRawBytes = kTileRows * kTK + kTileRows * kTK / 2;   // 24576
+constexpr int kABytes = kTileRows * kTK * 2;                       // 32768
 constexpr int kDecodeWarps = 16;         // 512 threads: one (row, 16-column chunk) each per K block
 constexpr int kFirstDecodeWarp = 4, kFirstEpiWarp = kFirstDecodeWarp + kDecodeWarps;
 constexpr int kGemmThreads = (kFirstEpiWarp + 4) * 32;
+constexpr int kGroupThreads = kDecodeWarps * 32 / kDecodeGroups;            // 128
+constexpr int kItemsPerThread = kTileRows * 4 / kGroupThreads;               // 4 when kTileRows == 128
+static_assert((kGroupThreads / 4) % 8 == 0, "row step must keep the swizzle phase");
 
 struct GemmParams {
     const int32_t* row_off;     // null: escapes stay "wrong"
     const int32_t* cols;
     const int16_t* correct;
     float* out;
-    float* ws;                  // [grid][2][BN][128] partial accumulators
+    float* ws;                  // [grid][2][BN][256] partial accumulators
     unsigned int* status;
     int M, K, B, out_stride;
     int BN;                     // sequences per tile (multiple of 16, <= 256)
@@ -141,7 +156,7 @@ __device__ __forceinline__ void decode_item(const uint8_t* raw, uint8_t* A, int 
                                             uint32_t base2, const GemmParams& P, int m0, int k0)
 {
     const uint4 s = *reinterpret_cast<const uint4*>(raw + item * 16);
-    const uint2 g = *reinterpret_cast<const uint2*>(raw + kTM * kTK + item * 8);
+    const uint2 g = *reinterpret_cast<const uint2*>(raw + kTileRows * kTK + item * 8);
     uint32_t p[4], lo[4], hi[4];
     decode8<kMode>(s.x, s.y, g.x, base2, p);
     lo[0] = prmt(p[0], p[1], 0x5410u); lo[1] = prmt(p[2], p[3], 0x5410u);
@@ -181,27 +196,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const int BN = P.BN;
     const uint32_t xbytes = (uint32_t)BN * 128u;
-    uint8_t* raw = smem;                                         // [kRawStages][12288]
-    uint8_t* Abuf = raw + kRawStages * kRawBytes;                // [kOpStages][16384]
-    uint8_t* Xbuf = Abuf + kOpStages * kABytes;                  // [kOpStages][BN*128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(Xbuf + (size_t)kOpStages * xbytes);
+    uint8_t* raw = smem;                                         // [kRawStages][24576]
+    uint8_t* Abuf = raw + kRawStages * kRawBytes;                // [kAStages][kHalves x 16384]
+    uint8_t* Xbuf = Abuf + kAStages * kABytes;                   // [kXStages][BN*128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Xbuf + (size_t)kXStages * xbytes);
     const uint32_t b_rawfull = smem_addr(bars);                  // [kRawStages]
     const uint32_t b_rawempty = b_rawfull + 8 * kRawStages;      // [kRawStages]
-    const uint32_t b_afull = b_rawempty + 8 * kRawStages;        // [kOpStages]
-    const uint32_t b_xfull = b_afull + 8 * kOpStages;            // [kOpStages]
-    const uint32_t b_consumed = b_xfull + 8 * kOpStages;         // [kOpStages]  MMA done with A/X stage
-    const uint32_t b_accfull = b_consumed + 8 * kOpStages;       // [2]
+    const uint32_t b_afull = b_rawempty + 8 * kRawStages;        // [kAStages]
+    const uint32_t b_afree = b_afull + 8 * kAStages;             // [kAStages]  MMA done with the A stage
+    const uint32_t b_xfull = b_afree + 8 * kAStages;             // [kXStages]
+    const uint32_t b_xfree = b_xfull + 8 * kXStages;             // [kXStages]  MMA done with the X stage
+    const uint32_t b_accfull = b_xfree + 8 * kXStages;           // [2]
     const uint32_t b_accempty = b_accfull + 16;                  // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kRawStages + 3 * kOpStages + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
 
     __shared__ int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int i = 0; i < kRawStages; i++) { mbar_init(b_rawfull + 8 * i, 1); mbar_init(b_rawempty + 8 * i, kDecodeWarps); }
-        for (int i = 0; i < kOpStages; i++) {
-            mbar_init(b_afull + 8 * i, kDecodeWarps); mbar_init(b_xfull + 8 * i, 1); mbar_init(b_consumed + 8 * i, 1);
-        }
+        for (int i = 0; i < kRawStages; i++) { mbar_init(b_rawfull + 8 * i, 1); mbar_init(b_rawempty + 8 * i, kDecodeWarps / kDecodeGroups); }
+        for (int i = 0; i < kAStages; i++) { mbar_init(b_afull + 8 * i, kDecodeWarps / kDecodeGroups); mbar_init(b_afree + 8 * i, 1); }
+        for (int i = 0; i < kXStages; i++) { mbar_init(b_xfull + 8 * i, 1); mbar_init(b_xfree + 8 * i, 1); }
         for (int i = 0; i < 2; i++) { mbar_init(b_accfull + 8 * i, 1); mbar_init(b_accempty + 8 * i, 4); }
         mbar_fence_init();
     }
@@ -215,26 +230,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
     const int KB = P.KB;
     const Range rg = cta_range((long long)P.n_mtiles * P.n_ntiles * KB, gridDim.x, blockIdx.x);
     const int tile0 = rg.lo / KB, kb0 = rg.lo - tile0 * KB;     // the only divisions of the schedule
-    const bool two_acc = 2 * BN <= (int)P.tmem_cols;             // accumulators are double buffered
+    const bool two_acc = 2 * kHalves * BN <= (int)P.tmem_cols;   // accumulators are double buffered
 
     if (warp == 0) {
-        // ------------------------------ producer ------------------------------
+        // ------------------------------ raw-tile producer ---------------------
+        // weights are never written, so this loop does not wait for the predecessor kernel
         if (lane == 0) {
-            grid_dependency_wait();                              // activations come from the predecessor
-            int sr = 0, so = 0, tile = tile0, kb = kb0;
+            int sr = 0, tile = tile0, kb = kb0;
             int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
-            uint32_t wr = 0, wo = 0;
+            uint32_t wr = 0;
             for (int it = rg.lo; it < rg.hi; it++) {
                 if (wr > 0) mbar_wait(b_rawempty + 8 * sr, (wr - 1) & 1, P.status, 0x10u, &s_abort);
                 mbar_arrive_expect_tx(b_rawfull + 8 * sr, kRawBytes);
                 const uint32_t rdst = smem_addr(raw + sr * kRawBytes);
-                tma_load_2d(rdst, &map_sm, kb * kTK, mt * kTM, b_rawfull + 8 * sr);
-                tma_load_2d(rdst + kTM * kTK, &map_gr, kb * (kTK / 2), mt * kTM, b_rawfull + 8 * sr);
-                if (wo > 0) mbar_wait(b_consumed + 8 * so, (wo - 1) & 1, P.status, 0x20u, &s_abort);
-                mbar_arrive_expect_tx(b_xfull + 8 * so, xbytes);
-                tma_load_2d(smem_addr(Xbuf + (size_t)so * xbytes), &map_x, kb * kTK, nt * BN, b_xfull + 8 * so);
+                tma_load_2d(rdst, &map_sm, kb * kTK, mt * kTileRows, b_rawfull + 8 * sr);
+                tma_load_2d(rdst + kTileRows * kTK, &map_gr, kb * (kTK / 2), mt * kTileRows, b_rawfull + 8 * sr);
                 if (++sr == kRawStages) { sr = 0; wr++; }
-                if (++so == kOpStages) { so = 0; wo++; }
+                if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mt++; } }
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------ activation-tile producer --------------
+        if (lane == 0) {
+            grid_dependency_wait();                              // activations come from the predecessor
+            int sx = 0, tile = tile0, kb = kb0;
+            int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+            uint32_t wx = 0;
+            for (int it = rg.lo; it < rg.hi; it++) {
+                if (wx > 0) mbar_wait(b_xfree + 8 * sx, (wx - 1) & 1, P.status, 0x20u, &s_abort);
+                mbar_arrive_expect_tx(b_xfull + 8 * sx, xbytes);
+                tma_load_2d(smem_addr(Xbuf + (size_t)sx * xbytes), &map_x, kb * kTK, nt * BN, b_xfull + 8 * sx);
+                if (++sx == kXStages) { sx = 0; wx++; }
                 if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mt++; } }
             }
         }
@@ -242,29 +268,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
         // ------------------------------ MMA issuer ----------------------------
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
-            int so = 0, nacc = 0, it = rg.lo, tile_end = (tile0 + 1) * KB;
-            uint32_t wo = 0;
+            int sa = 0, sx = 0, nacc = 0, it = rg.lo, tile_end = (tile0 + 1) * KB;
+            uint32_t wa = 0, wx = 0;
             while (it < rg.hi) {
                 const int seg_end = tile_end < rg.hi ? tile_end : rg.hi;
                 const int buf = two_acc ? (nacc & 1) : 0;
                 const int uses = two_acc ? (nacc >> 1) : nacc;    // earlier uses of this accumulator
                 if (uses > 0) mbar_wait(b_accempty + 8 * buf, (uses - 1) & 1, P.status, 0x40u, &s_abort);
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kHalves * BN);
                 uint32_t accumulate = 0;
                 for (; it < seg_end; it++) {
-                    mbar_wait(b_afull + 8 * so, wo & 1, P.status, 0x80u, &s_abort);
-                    mbar_wait(b_xfull + 8 * so, wo & 1, P.status, 0x100u, &s_abort);
+                    mbar_wait(b_afull + 8 * sa, wa & 1, P.status, 0x80u, &s_abort);
+                    mbar_wait(b_xfull + 8 * sx, wx & 1, P.status, 0x100u, &s_abort);
                     tc_fence_after();
-                    const uint64_t ad = smem_desc_sw128(smem_addr(Abuf + so * kABytes));
-                    const uint64_t bd = smem_desc_sw128(smem_addr(Xbuf + (size_t)so * xbytes));
+                    const uint64_t bd = smem_desc_sw128(smem_addr(Xbuf + (size_t)sx * xbytes));
 #pragma unroll
-                    for (int k = 0; k < kTK / 16; k++) {
-                        umma_bf16(d_tmem, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc, accumulate);
-                        accumulate = 1;
+                    for (int h = 0; h < kHalves; h++) {
+                        const uint64_t ad = smem_desc_sw128(smem_addr(Abuf + sa * kABytes + h * (kTM * kTK * 2)));
+#pragma unroll
+                        for (int k = 0; k < kTK / 16; k++)
+                            umma_bf16(d_tmem + (uint32_t)(h * BN), ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc,
+                                      k == 0 ? accumulate : 1u);
                     }
-                    umma_commit(b_consumed + 8 * so);            // frees the A and X stage when these MMAs finish
-                    if (++so == kOpStages) { so = 0; wo++; }
+                    accumulate = 1;
+                    umma_commit(b_afree + 8 * sa);               // both stages are free when these MMAs finish
+                    umma_commit(b_xfree + 8 * sx);
+                    if (++sa == kAStages) { sa = 0; wa++; }
+                    if (++sx == kXStages) { sx = 0; wx++; }
                 }
                 umma_commit(b_accfull + 8 * buf);                // accumulator of this tile segment is complete
                 nacc++;
@@ -273,25 +304,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
         }
     } else if (warp >= kFirstDecodeWarp && warp < kFirstEpiWarp) {
         // ------------------------------ decode --------------------------------
-        const int item = threadIdx.x - kFirstDecodeWarp * 32;     // 0..511 = row*4 + chunk
-        const int r = item >> 2, c = item & 3, sw = r & 7;
+        // kDecodeGroups groups of warps take K blocks in turn (group = block index
+        // mod kDecodeGroups) and each group owns one A stage, so a group has
+        // kDecodeGroups MMA periods for the wait -> load -> decode -> store ->
+        // fence -> arrive chain of its block, and a thread amortises that chain
+        // over kItemsPerThread (row, 16-column chunk) items.
+        const int dt = threadIdx.x - kFirstDecodeWarp * 32;
+        const int gi = dt / kGroupThreads, t = dt % kGroupThreads;
+        const int r = t >> 2, c = t & 3, sw = r & 7;              // row advances by kGroupThreads/4 per item, so r&7 is fixed
         const uint32_t off_lo = r * 128 + (((2 * c) ^ sw) << 4), off_hi = r * 128 + (((2 * c + 1) ^ sw) << 4);
-        int sr = 0, so = 0, tile = tile0, kb = kb0;
-        int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
-        uint32_t wr = 0, wo = 0;
-        for (int it = rg.lo; it < rg.hi; it++) {
+        int sr = gi % kRawStages, tile = tile0, kb = kb0 + gi;
+        uint32_t wr = gi / kRawStages, wo = 0;
+        while (kb >= KB) { kb -= KB; tile++; }
+        int mt = tile / P.n_ntiles;
+        uint8_t* Ap = Abuf + gi * kABytes;
+        for (int it = rg.lo + gi; it < rg.hi; it += kDecodeGroups) {
             mbar_wait(b_rawfull + 8 * sr, wr & 1, P.status, 0x200u, &s_abort);
-            if (wo > 0) mbar_wait(b_consumed + 8 * so, (wo - 1) & 1, P.status, 0x400u, &s_abort);
+            if (wo > 0) mbar_wait(b_afree + 8 * gi, (wo - 1) & 1, P.status, 0x400u, &s_abort);
             const uint8_t* rawp = raw + sr * kRawBytes;
-            uint8_t* Ap = Abuf + so * kABytes;
-            if (P.neg_base) decode_item<1>(rawp, Ap, item, off_lo, off_hi, P.base2, P, mt * kTM, kb * kTK);
-            else decode_item<0>(rawp, Ap, item, off_lo, off_hi, P.base2, P, mt * kTM, kb * kTK);
+#pragma unroll
+            for (int j = 0; j < kItemsPerThread; j++) {
+                const int item = t + j * kGroupThreads;
+                const uint32_t o2 = j * (kGroupThreads / 4) * 128;
+                if (P.neg_base) decode_item<1>(rawp, Ap, item, off_lo + o2, off_hi + o2, P.base2, P, mt * kTileRows, kb * kTK);
+                else decode_item<0>(rawp, Ap, item, off_lo + o2, off_hi + o2, P.base2, P, mt * kTileRows, kb * kTK);
+            }
             fence_async_smem();                                   // generic-proxy writes -> visible to the MMA
             __syncwarp();
-            if (lane == 0) { mbar_arrive(b_afull + 8 * so); mbar_arrive(b_rawempty + 8 * sr); }
-            if (++sr == kRawStages) { sr = 0; wr++; }
-            if (++so == kOpStages) { so = 0; wo++; }
-            if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mt++; } }
+            if (lane == 0) { mbar_arrive(b_afull + 8 * gi); mbar_arrive(b_rawempty + 8 * sr); }
+            sr += kDecodeGroups;
+            while (sr >= kRawStages) { sr -= kRawStages; wr++; }
+            wo++;
+            kb += kDecodeGroups;
+            if (kb >= KB) {
+                while (kb >= KB) { kb -= KB; tile++; }
+                mt = tile / P.n_ntiles;
+            }
         }
     } else if (warp >= kFirstEpiWarp) {
         // ------------------------------ epilogue ------------------------------
@@ -308,15 +356,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
             const int uses = two_acc ? (nacc >> 1) : nacc;
             mbar_wait(b_accfull + 8 * buf, uses & 1, P.status, 0x800u, &s_abort);
             tc_fence_after();
-            const int m = mt * kTM + mrow;
             const int b0 = nt * BN;
             // A segment that covers only part of its tile's K range goes to the
             // workspace (slot 0: the tile this CTA's range starts in, slot 1: the
             // tile it ends in) and is summed by gemm_reduce_kernel.
-            float* wsp = P.ws + ((size_t)blockIdx.x * 2 + (it == rg.lo ? 0 : 1)) * (size_t)BN * kTM;
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            float* wsp = P.ws + ((size_t)blockIdx.x * 2 + (it == rg.lo ? 0 : 1)) * (size_t)BN * kTileRows;
+            for (int hc = 0; hc < kHalves * ((BN + 31) / 32); hc++) {
+                const int nch = (BN + 31) / 32, h = hc / nch, c0 = (hc - h * nch) * 32;
+                const int m = mt * kTileRows + h * kTM + mrow;
+                const int tr = h * kTM + mrow;                    // row inside the CTA tile
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kHalves * BN + h * BN + c0), v);
                 tmem_ld_wait();
                 if (whole) {
                     if (m < P.M) {
@@ -327,7 +377,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; j++)
-                        if (c0 + j < BN) wsp[(size_t)(c0 + j) * kTM + mrow] = __uint_as_float(v[j]);
+                        if (c0 + j < BN) wsp[(size_t)(c0 + j) * kTileRows + tr] = __uint_as_float(v[j]);
                 }
             }
             tc_fence_before();
@@ -363,18 +413,19 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
     while (c_last + 1 < G && cta_range(T, G, c_last + 1).lo < tile_end) c_last++;
     if (c_first == c_last) return;
     const int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
-    const int m4 = (threadIdx.x & 31) * 4;                       // four consecutive rows per thread
+    constexpr int kRowLanes = kTileRows / 4;                     // threads across the rows of a tile
+    const int m4 = (threadIdx.x % kRowLanes) * 4;                // four consecutive rows per thread
     const int b0 = nt * BN;
-    for (int j = blockIdx.y * 32 + (threadIdx.x >> 5); j < blockIdx.y * 32 + 32 && j < BN; j += 8) {
+    for (int j = blockIdx.y * 32 + threadIdx.x / kRowLanes; j < blockIdx.y * 32 + 32 && j < BN; j += 256 / kRowLanes) {
         if (b0 + j >= P.B) break;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int c = c_first; c <= c_last; c++) {
             const int slot = cta_range(T, G, c).lo >= tile_lo ? 0 : 1;
             const float4 v = __ldcg(reinterpret_cast<const float4*>(
-                P.ws + ((size_t)c * 2 + slot) * (size_t)BN * kTM + (size_t)j * kTM + m4));
+                P.ws + ((size_t)c * 2 + slot) * (size_t)BN * kTileRows + (size_t)j * kTileRows + m4));
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        const int m = mt * kTM + m4;
+        const int m = mt * kTileRows + m4;
         float* dst = P.out + (size_t)(b0 + j) * P.out_stride + m;
         if (m + 3 < P.M && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
             *reinterpret_cast<float4*>(dst) = acc;
@@ -390,6 +441,12 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
 // ----------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------
+static size_t gemm_smem_bytes(int BN)
+{
+    return (size_t)kRawStages * kRawBytes + (size_t)kAStages * kABytes + (size_t)kXStages * BN * 128 +
+           8 * kNumBars + 16 + 1024;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -466,21 +523,21 @@ int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* ou
     P.out = (float*)out; P.M = w->M; P.K = w->K; P.B = B; P.out_stride = out_stride;
     P.BN = B >= 256 ? 256 : ((B + 15) / 16) * 16;
     if (P.BN < 32) P.BN = 32;
-    P.n_mtiles = (w->M + kTM - 1) / kTM;
+    P.n_mtiles = (w->M + kTileRows - 1) / kTileRows;
     P.n_ntiles = (B + P.BN - 1) / P.BN;
     P.KB = (w->K + kTK - 1) / kTK;
     P.base2 = make_base2(w->base_exp);
     P.neg_base = w->base_exp < 0;
     uint32_t cols = 32;
-    while (cols < (uint32_t)(2 * P.BN) && cols < 512) cols <<= 1;
+    while (cols < (uint32_t)(2 * kHalves * P.BN) && cols < 512) cols <<= 1;
     P.tmem_cols = cols;
     P.status = device_status_word();
 
     CUtensorMap msm, mgr, mx;
     if (!make_map(&msm, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->sm, (uint64_t)w->K, (uint64_t)w->M, (uint64_t)w->K,
-                  kTK, kTM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                  kTK, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !make_map(&mgr, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->gr, (uint64_t)w->K / 2, (uint64_t)w->M, (uint64_t)w->K / 2,
-                  kTK / 2, kTM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                  kTK / 2, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)w->K, (uint64_t)B, (uint64_t)act_stride * 2,
                   kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
@@ -494,15 +551,14 @@ int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* ou
     if (T / grid < min_iters) grid = (int)((T + min_iters - 1) / min_iters);
     if (grid < 1) grid = 1;
     Scratch sc;
-    int rc = get_scratch((size_t)sms * 2 * 256 * kTM * sizeof(float), sc, who);   // sized for the largest launch
+    int rc = get_scratch((size_t)sms * 2 * 256 * kTileRows * sizeof(float), sc, who);   // sized for the largest launch
     if (rc) return rc;
     P.ws = sc.ws;
     // does any tile have its K range shared between CTAs?
     bool partial = false;
     for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(T, grid, c).hi % P.KB != 0;
 
-    const size_t smem = (size_t)kRawStages * kRawBytes + (size_t)kOpStages * kABytes + (size_t)kOpStages * P.BN * 128 +
-                        8 * (2 * kRawStages + 3 * kOpStages + 4) + 16 + 1024;
+    const size_t smem = gemm_smem_bytes(P.BN);
     static bool attr_set[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -607,13 +663,13 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     P.out = (float*)out; P.M = w->M; P.K = w->K; P.B = B; P.out_stride = out_stride;
     P.BN = ((B + 15) / 16) * 16;
     if (P.BN < 32) P.BN = 32;
-    P.n_mtiles = (w->M + kTM - 1) / kTM;
+    P.n_mtiles = (w->M + kTileRows - 1) / kTileRows;
     P.n_ntiles = 1;
     P.KB = (w->K + kTK - 1) / kTK;
     P.base2 = make_base2(w->base_exp);
     P.neg_base = w->base_exp < 0;
     uint32_t cols = 32;
-    while (cols < (uint32_t)(2 * P.BN) && cols < 512) cols <<= 1;
+    while (cols < (uint32_t)(2 * kHalves * P.BN) && cols < 512) cols <<= 1;
     P.tmem_cols = cols;
     P.status = st.status;
     P.ws = st.ws;
@@ -622,9 +678,9 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: M*K exceeds the tile schedule's range", who);
     CUtensorMap msm, mgr, mx;
     if (!make_map(&msm, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->sm, (uint64_t)w->K, (uint64_t)w->M, (uint64_t)w->K,
-                  kTK, kTM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                  kTK, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !make_map(&mgr, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->gr, (uint64_t)w->K / 2, (uint64_t)w->M, (uint64_t)w->K / 2,
-                  kTK / 2, kTM, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                  kTK / 2, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)w->K, (uint64_t)B, (uint64_t)act_stride * 2,
                   kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
@@ -633,15 +689,14 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     const int sms = sm_count();
     int grid = T < sms ? (int)T : sms;
     if (T / grid < 8) grid = (int)((T + 7) / 8);
-    const size_t per_cta = (size_t)2 * P.BN * kTM;
+    const size_t per_cta = (size_t)2 * P.BN * kTileRows;
     const int fit = (int)(kNoAllocWsFloats / per_cta);
     if (grid > fit) grid = fit;
     if (grid < 1) grid = 1;
     bool partial = false;
     for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(T, grid, c).hi % P.KB != 0;
 
-    const size_t smem = (size_t)kRawStages * kRawBytes + (size_t)kOpStages * kABytes + (size_t)kOpStages * P.BN * 128 +
-                        8 * (2 * kRawStages + 3 * kOpStages + 4) + 16 + 1024;
+    const size_t smem = gemm_smem_bytes(P.BN);
     rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, msm, mgr, mx, P);
     if (rc || !partial) return rc;
     return launch(gemm_reduce_kernel, dim3(P.n_mtiles, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
