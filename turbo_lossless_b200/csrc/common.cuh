@@ -225,6 +225,22 @@ __device__ __forceinline__ void decode8(uint32_t s_lo, uint32_t s_hi, uint32_t g
     }
 }
 
+// Same decode as decode8<0>, with the three shifts expressed as multiplications
+// by values the compiler cannot see (kernel parameters holding 128, 8 and
+// 1<<24): they are then issued as integer multiply-adds on the FMA pipe, which
+// has spare issue slots in the HBM-bound kernels, instead of shift-adds on the
+// ALU pipe, which is their busiest pipe.
+struct DecodeMul { uint32_t m128, m8, hi24; };
+__device__ __forceinline__ void decode8_fma(uint32_t s_lo, uint32_t s_hi, uint32_t g, uint32_t base2,
+                                            const DecodeMul& k, uint32_t (&p)[4])
+{
+    const uint32_t g8 = __umulhi(g, k.hi24);            // g >> 8
+    p[0] = and_or(prmt(s_lo, s_hi, 0xC480u), 0x807F807Fu, (g  & 0x000F000Fu) * k.m128 + base2);
+    p[1] = and_or(prmt(s_lo, s_hi, 0xD591u), 0x807F807Fu, (g  & 0x00F000F0u) * k.m8 + base2);
+    p[2] = and_or(prmt(s_lo, s_hi, 0xE6A2u), 0x807F807Fu, (g8 & 0x000F000Fu) * k.m128 + base2);
+    p[3] = and_or(prmt(s_lo, s_hi, 0xF7B3u), 0x807F807Fu, (g8 & 0x00F000F0u) * k.m8 + base2);
+}
+
 // Non-zero iff one of the eight nibbles of g is zero (an escape is present).
 __device__ __forceinline__ uint32_t zero_nibbles(uint32_t g)
 {

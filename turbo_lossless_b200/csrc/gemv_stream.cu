@@ -77,6 +77,7 @@ struct StreamParams {
     int depth;              // ring stages
     int total_blocks;
     unsigned int* status;
+    DecodeMul mul;          // {128, 8, 1<<24}: see decode8_fma
 };
 
 struct BlockRef { int ti; int r0; };
@@ -108,7 +109,7 @@ __device__ __forceinline__ BlockRef locate_block(const StreamParams& P, int blk)
 // an SM, so two CTAs share it -- of one launch, or, under programmatic
 // dependent launch, the last CTAs of one launch and the first of the next,
 // whose producer then fills its ring while the predecessor drains.
-template <int kMode, int kGroups>
+template <int kMode, int kGroups, bool kSwap>
 __global__ void __launch_bounds__(stream_threads(kGroups), kGroups == 1 ? 2 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams P)
 {
@@ -223,7 +224,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         // order (and swap them back in registers): in every 8-lane phase of a
         // 16-byte load the even-g lanes then hit the low 64 bytes of the window
         // and the odd-g lanes the high 64 bytes.
-        const uint32_t odd = g & 1;
+        const uint32_t odd = kSwap ? (g & 1) : 0u;   // kSwap off: plain order, two-way conflicts, no selects
         const uint32_t offA = (rA * Q + qA) * kSegCols + wi * 128 + t4 * 16;
         const uint32_t offB = (rB * Q + qB) * kSegCols + wi * 128 + t4 * 16;
         const uint32_t goffA = kGrBase + (rA * Q + qA) * (kSegCols / 2) + wi * 64 + t4 * 8;
@@ -273,8 +274,13 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 uint32_t pa[4], pb[4];
-                decode8<kMode>(sa[2 * j], sa[2 * j + 1], gaw[j], base2, pa);
-                decode8<kMode>(sb[2 * j], sb[2 * j + 1], gbw[j], base2, pb);
+                if (kMode == 0) {
+                    decode8_fma(sa[2 * j], sa[2 * j + 1], gaw[j], base2, P.mul, pa);
+                    decode8_fma(sb[2 * j], sb[2 * j + 1], gbw[j], base2, P.mul, pb);
+                } else {
+                    decode8<kMode>(sa[2 * j], sa[2 * j + 1], gaw[j], base2, pa);
+                    decode8<kMode>(sb[2 * j], sb[2 * j + 1], gbw[j], base2, pb);
+                }
                 mma_bf16_16816(acc[0], pa[0], pb[0], pa[1], pb[1], xq[j].x, xq[j].y);
                 mma_bf16_16816(acc[1], pa[2], pb[2], pa[3], pb[3], xq[j].z, xq[j].w);
             }
@@ -395,6 +401,7 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     }
     P.total_blocks = blocks;
     P.status = device_status_word();
+    P.mul.m128 = 128u; P.mul.m8 = 8u; P.mul.hi24 = 1u << 24;
 
     // Shape of the launch: consumer groups per CTA and CTAs per SM (tuning knobs
     // S12_GEMV_GROUPS / S12_GEMV_CTAS).  Default: one group, two CTAs per SM.
@@ -411,7 +418,7 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         cudaFuncAttributes fa;
-        static_smem = cudaFuncGetAttributes(&fa, gemv_stream_kernel<0, 1>) == cudaSuccess ? (int)fa.sharedSizeBytes : 1024;
+        static_smem = cudaFuncGetAttributes(&fa, gemv_stream_kernel<0, 1, true>) == cudaSuccess ? (int)fa.sharedSizeBytes : 1024;
     }
     // dynamic shared memory one CTA may use: everything, or what lets two CTAs (1 KB reserved each) share an SM
     const int per_cta = (ctas == 2 ? (optin + 1024) / 2 - 1024 : optin) - static_smem - 64;
@@ -428,18 +435,21 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     const size_t smem = fixed + (size_t)depth * kStageBytes;
 
     typedef void (*Kern)(const StreamParams);
-    static const Kern table[2][3] = {
-        {gemv_stream_kernel<0, 1>, gemv_stream_kernel<1, 1>, gemv_stream_kernel<2, 1>},
-        {gemv_stream_kernel<0, 2>, gemv_stream_kernel<1, 2>, gemv_stream_kernel<2, 2>}};
-    Kern kern = table[groups - 1][mode];
-    static bool attr_set[64][2][3];
+    const int swap = env_int2("S12_GEMV_SWAP", 0) ? 1 : 0;   // 0: plain load order (fewer instructions, measured faster)
+    static const Kern table[2][2][3] = {
+        {{gemv_stream_kernel<0, 1, false>, gemv_stream_kernel<1, 1, false>, gemv_stream_kernel<2, 1, false>},
+         {gemv_stream_kernel<0, 2, false>, gemv_stream_kernel<1, 2, false>, gemv_stream_kernel<2, 2, false>}},
+        {{gemv_stream_kernel<0, 1, true>, gemv_stream_kernel<1, 1, true>, gemv_stream_kernel<2, 1, true>},
+         {gemv_stream_kernel<0, 2, true>, gemv_stream_kernel<1, 2, true>, gemv_stream_kernel<2, 2, true>}}};
+    Kern kern = table[swap][groups - 1][mode];
+    static bool attr_set[64][4][3];
     int dev = 0;
     cudaGetDevice(&dev);
     dev = (dev < 0 || dev >= 64) ? 0 : dev;
-    if (!attr_set[dev][groups - 1][mode]) {
+    if (!attr_set[dev][swap * 2 + groups - 1][mode]) {
         int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - static_smem - 64), who);
         if (rc) { *rc_out = rc; return -1; }
-        attr_set[dev][groups - 1][mode] = true;
+        attr_set[dev][swap * 2 + groups - 1][mode] = true;
     }
     const int slots = sms * ctas;
     const int grid = blocks < slots ? blocks : slots;
