@@ -46,10 +46,14 @@ constexpr int kSegCols      = 1024;
 constexpr int kGrBase       = 16 * kSegCols;                             // gr part of a stage
 constexpr int kStageBytes   = kGrBase + 16 * (kSegCols / 2);             // 24576: dense image of the tile
 constexpr int kGroupWarps   = 8;        // warps per consumer group: 128 columns of every segment each
-constexpr int kXChunkUnits  = kSegCols / 8 + 4;   // 16-byte units per activation chunk incl. 64 B stagger
+constexpr int kXChunkUnits  = kSegCols / 8;       // 16-byte units per activation chunk
+// chunk c starts 64 B (4 units) further than an even/odd pair would put it, so that the two chunks
+// read in one 8-lane phase (an even chunk and its odd successor) fall on different banks
+__host__ __device__ constexpr int xchunk_base(int c) { return c * kXChunkUnits + ((c + 1) >> 1) * 4; }
+__host__ __device__ constexpr int xunits_total(int nchunks) { return xchunk_base(nchunks); }
 constexpr int kEpiWarps     = 2;
 constexpr int stream_threads(int groups) { return (groups * kGroupWarps + 1 + kEpiWarps) * 32; }
-constexpr int kRedSlots     = 24;       // row blocks whose partial sums may be pending
+constexpr int kRedSlots     = 16;       // row blocks whose partial sums may be pending (power of two)
 constexpr int kMaxDepth     = 8;
 
 static_assert(kStageBytes % 128 == 0, "stage alignment");
@@ -78,20 +82,24 @@ struct StreamParams {
     int total_blocks;
     unsigned int* status;
     DecodeMul mul;          // {128, 8, 1<<24}: see decode8_fma
+#ifdef S12_TRACE
+    int trace_slot;
+#endif
 };
 
 struct BlockRef { int ti; int r0; };
 
 #ifdef S12_TRACE
 // Development aid: per-CTA timestamps (ns) of kernel phases.
-__device__ unsigned long long g_trace[148 * 8];
+__device__ unsigned long long g_trace[4][148 * 8];
+int g_trace_slot_host = 0;
 __device__ __forceinline__ unsigned long long now_ns()
 {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-#define S12_STAMP(slot) do { if (lane == 0 && blockIdx.x < 148) g_trace[blockIdx.x * 8 + (slot)] = now_ns(); } while (0)
+#define S12_STAMP(slot) do { if (lane == 0 && blockIdx.x < 148) g_trace[P.trace_slot & 3][blockIdx.x * 8 + (slot)] = now_ns(); } while (0)
 #else
 #define S12_STAMP(slot) do { } while (0)
 #endif
@@ -116,7 +124,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
     constexpr int kConsumers = kGroups * kGroupWarps;
     extern __shared__ __align__(128) uint8_t smem[];
     const int depth = P.depth;
-    const int xunits = P.tpr * P.Q * kXChunkUnits;               // 16-byte units of permuted x
+    const int xunits = xunits_total(P.tpr * P.Q);                // 16-byte units of permuted x
     uint8_t* ring = smem;
     uint4* xperm = reinterpret_cast<uint4*>(smem + (size_t)depth * kStageBytes);
     float* red = reinterpret_cast<float*>(xperm + xunits);       // [kRedSlots][kConsumers][16]
@@ -206,7 +214,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             // loads j = 0..3, each from position j*4 + t4
             const int c = u >> 7, uu = u & 127, w16 = uu & 15;
             const int pos = (((w16 >> 3) << 1) + (w16 & 1)) * 4 + ((w16 & 7) >> 1);
-            xperm[c * kXChunkUnits + (uu & ~15) + pos] = pv;
+            xperm[xchunk_base(c) + (uu & ~15) + pos] = pv;
         }
         named_bar_sync(1, kConsumers * 32);
         if (warp == 0) S12_STAMP(2);
@@ -256,7 +264,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             const uint4 bs = *reinterpret_cast<const uint4*>(st + offB + second);
             const uint2 gbf = *reinterpret_cast<const uint2*>(st + goffB + (first >> 1));
             const uint2 gbs = *reinterpret_cast<const uint2*>(st + goffB + (second >> 1));
-            const uint4* xp = xperm + ((kt * Q + qx) * kXChunkUnits + wi * 16 + t4);
+            const uint4* xp = xperm + (xchunk_base(kt * Q + qx) + wi * 16 + t4);
             uint4 xq[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) xq[j] = xp[j * 4];
@@ -402,6 +410,9 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     P.total_blocks = blocks;
     P.status = device_status_word();
     P.mul.m128 = 128u; P.mul.m8 = 8u; P.mul.hi24 = 1u << 24;
+#ifdef S12_TRACE
+    P.trace_slot = g_trace_slot_host;
+#endif
 
     // Shape of the launch: consumer groups per CTA and CTAs per SM (tuning knobs
     // S12_GEMV_GROUPS / S12_GEMV_CTAS).  Default: one group, two CTAs per SM.
@@ -410,7 +421,7 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     int ctas = groups == 2 ? 1 : env_int2("S12_GEMV_CTAS", 2);
     ctas = ctas == 1 ? 1 : 2;
     const int consumers = groups * kGroupWarps;
-    const size_t fixed = (size_t)P.tpr * Q * kXChunkUnits * 16 + (size_t)kRedSlots * consumers * 16 * sizeof(float) +
+    const size_t fixed = (size_t)xunits_total(P.tpr * Q) * 16 + (size_t)kRedSlots * consumers * 16 * sizeof(float) +
                          8 * (2 * kMaxDepth + 2 * kRedSlots);
     static int optin = 0, static_smem = 0;
     if (!optin) {
@@ -421,12 +432,12 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
         static_smem = cudaFuncGetAttributes(&fa, gemv_stream_kernel<0, 1, true>) == cudaSuccess ? (int)fa.sharedSizeBytes : 1024;
     }
     // dynamic shared memory one CTA may use: everything, or what lets two CTAs (1 KB reserved each) share an SM
-    const int per_cta = (ctas == 2 ? (optin + 1024) / 2 - 1024 : optin) - static_smem - 64;
+    const int per_cta = (ctas == 2 ? (optin + 1024) / 2 - 1024 : optin) - static_smem;
     if ((size_t)per_cta < fixed + 2 * (size_t)kStageBytes) {
         if (ctas == 2) ctas = 1;            // long rows: the activation vector needs the room
         else return 0;
     }
-    const int budget = (ctas == 2 ? (optin + 1024) / 2 - 1024 : optin) - static_smem - 64;
+    const int budget = (ctas == 2 ? (optin + 1024) / 2 - 1024 : optin) - static_smem;
     if ((size_t)budget < fixed + 2 * (size_t)kStageBytes) return 0;   // K too large for this layout
     int depth = (int)(((size_t)budget - fixed) / kStageBytes);
     if (depth > kMaxDepth) depth = kMaxDepth;
@@ -447,7 +458,7 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     cudaGetDevice(&dev);
     dev = (dev < 0 || dev >= 64) ? 0 : dev;
     if (!attr_set[dev][swap * 2 + groups - 1][mode]) {
-        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - static_smem - 64), who);
+        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - static_smem), who);
         if (rc) { *rc_out = rc; return -1; }
         attr_set[dev][swap * 2 + groups - 1][mode] = true;
     }
