@@ -219,9 +219,8 @@ def run_ours(args):
             eng.gemv(ws, x, outs)
             launches[0] += 1
         else:
-            for w, o in zip(ws, outs):
-                eng.gemm(w, x, o, x.shape[1], o.shape[1], B)
-                launches[0] += 1
+            eng.gemm_multi(ws, x, outs, x.shape[1], B)
+            launches[0] += 1
 
     # The step as a list of segments: ("k", fn) = our launches only (capturable as one CUDA graph),
     # ("ar", tensor) = the all-reduce after a row-parallel projection.  NCCL collectives are kept

@@ -188,6 +188,14 @@ int s12_gemv_batched_async(const S12Tensor* w, const void* act, int act_stride,
 int s12_gemm_async(const S12Tensor* w, const void* act, int act_stride,
                    void* out, int out_stride, int B, void* stream);
 
+/* Up to four tensors that share K and the activations (q/k/v, gate/up) as ONE
+ * tensor-core launch: their row tiles form one schedule, so small projections
+ * (the 1024-row k and v of a GQA model) do not leave SMs idle.  outs[i] is fp32
+ * [B][out_strides[i]].  Falls back to one s12_gemm_async per tensor when the
+ * tensor-core path does not apply. */
+int s12_gemm_multi_async(const S12Tensor* w, int num_tensors, const void* act, int act_stride,
+                         void* const* outs, const int* out_strides, int B, void* stream);
+
 /* Same result as s12_gemm_async for 17 <= B <= 256, for callers that must not
  * allocate device memory after start-up (a server that gave the whole GPU to
  * its own memory pool, a latency-critical loop that cannot afford cudaMalloc's

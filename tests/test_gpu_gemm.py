@@ -81,3 +81,22 @@ def test_zero_batch_and_bad_strides(eng, O):
                                                   None, None, None, None) == 0
     assert lib.nv_launch_split12_fused_gemm_async(*args, 100, out.data_ptr(), 128, 128, 256, 4, None,
                                                   None, None, None, None) < 0
+
+
+@pytest.mark.parametrize("B", [24, 64, 256])
+def test_multi_tensor_launch_qkv(eng, O, B):
+    """q/k/v-like tensors (own base_exp, own row counts, one with a ragged row count) in one launch."""
+    K = 1024
+    specs = [(512, 0.02, 1e-3), (130, 0.05, 5e-3), (128, 0.01, 0.0)]
+    ws, packs = [], []
+    for i, (M, std, frac) in enumerate(specs):
+        w = O.synth_weights(M, K, 200 + i, std=std, outlier_frac=frac)
+        ws.append(w); packs.append(O.pack(w))
+    x = O.synth_acts(B, K, 9)
+    xd = dev(x)
+    outs = [torch.full((B, p.M + 4), float("nan"), device="cuda") for p in packs]
+    eng.gemm_multi([_cw(p) for p in packs], xd, outs, K, B)
+    for w, p, o in zip(ws, packs, outs):
+        assert_close(o[:, :p.M], O.gemm_exact(w, x), what=f"M={p.M}")
+        assert torch.isnan(o[:, p.M:]).all()
+    assert eng.device_status() == 0

@@ -45,6 +45,7 @@ SIGNATURES = {
     "s12_gemv_async": (_i, [C.POINTER(S12Tensor), _i, _vp, C.POINTER(_vp), _vp]),
     "s12_gemv_batched_async": (_i, [C.POINTER(S12Tensor), _vp, _i, _vp, _i, _i, _vp]),
     "s12_gemm_async": (_i, [C.POINTER(S12Tensor), _vp, _i, _vp, _i, _i, _vp]),
+    "s12_gemm_multi_async": (_i, [C.POINTER(S12Tensor), _i, _vp, _i, C.POINTER(_vp), C.POINTER(_i), _i, _vp]),
     "s12_gemm_noalloc_async": (_i, [C.POINTER(S12Tensor), _vp, _i, _vp, _i, _i, _vp]),
     "s12_set_dependent_launch": (_i, [_i]),
     "s12_last_error": (C.c_char_p, []),

@@ -12,6 +12,9 @@ int gemm_tc_supported(const S12Tensor* w, int act_stride, int out_stride, int B)
 int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
                    int B, void* stream, const char* who);
 
+int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_stride, void* const* outs,
+                         const int* out_strides, int B, void* stream, const char* who);
+
 int gemm_dispatch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
                   int B, void* stream, const char* who)
 {
@@ -56,6 +59,29 @@ int s12_gemm_async(const S12Tensor* w, const void* act, int act_stride,
                    void* out, int out_stride, int B, void* stream)
 {
     return s12::gemm_dispatch(w, act, act_stride, out, out_stride, B, stream, "s12_gemm_async");
+}
+
+int s12_gemm_multi_async(const S12Tensor* w, int num_tensors, const void* act, int act_stride,
+                         void* const* outs, const int* out_strides, int B, void* stream)
+{
+    using namespace s12;
+    const char* who = "s12_gemm_multi_async";
+    if (!w || !outs || !out_strides || num_tensors < 1 || num_tensors > 4)
+        return fail(S12_ERR_BAD_ARG, "%s: bad tensor list", who);
+    bool tc = B > 16;
+    for (int i = 0; i < num_tensors; i++) {
+        if (w[i].K != w[0].K) return fail(S12_ERR_BAD_ARG, "%s: tensors of one launch must share K", who);
+        if (w[i].M < 1 || !outs[i] || out_strides[i] < w[i].M) return fail(S12_ERR_BAD_ARG, "%s: tensor %d: M, out or out_stride", who, i);
+        tc = tc && gemm_tc_supported(&w[i], act_stride, out_strides[i], B);
+    }
+    if (B == 0) return S12_OK;
+    if (B < 0 || !act || act_stride < w[0].K) return fail(S12_ERR_BAD_ARG, "%s: B, act or act_stride", who);
+    if (tc) return gemm_tc_launch_multi(w, num_tensors, act, act_stride, outs, out_strides, B, stream, who);
+    for (int i = 0; i < num_tensors; i++) {
+        int rc = gemm_dispatch(&w[i], act, act_stride, outs[i], out_strides[i], B, stream, who);
+        if (rc) return rc;
+    }
+    return S12_OK;
 }
 
 int nv_launch_split12_fused_gemm_async(const void* sm, const void* gr, int base_exp,

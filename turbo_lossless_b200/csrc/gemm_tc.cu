@@ -65,20 +65,39 @@ constexpr int kGroupThreads = kDecodeWarps * 32 / kDecodeGroups;            // 1
 constexpr int kItemsPerThread = kTileRows * 4 / kGroupThreads;               // 4 when kTileRows == 128
 static_assert((kGroupThreads / 4) % 8 == 0, "row step must keep the swizzle phase");
 
-struct GemmParams {
+constexpr int kMaxGemmTensors = 4;       // tensors sharing K and the activations in one launch (q/k/v, gate/up)
+
+struct GemmTensor {
     const int32_t* row_off;     // null: escapes stay "wrong"
     const int32_t* cols;
     const int16_t* correct;
     float* out;
-    float* ws;                  // [grid][2][BN][256] partial accumulators
-    unsigned int* status;
-    int M, K, B, out_stride;
-    int BN;                     // sequences per tile (multiple of 16, <= 256)
-    int n_mtiles, n_ntiles, KB; // KB = K blocks per tile
+    int M, out_stride;
     uint32_t base2;
-    int neg_base;               // base_exp < 0: decode mode 1
+    int mtile_end;              // exclusive end of this tensor's row tiles in the launch
+};
+
+struct GemmParams {
+    GemmTensor t[kMaxGemmTensors];
+    int nt;
+    float* ws;                  // [grid][2][BN][kTileRows] partial accumulators
+    unsigned int* status;
+    int K, B;
+    int BN;                     // sequences per tile (multiple of 16, <= 256)
+    int n_mtiles, n_ntiles, KB; // row tiles of all tensors, sequence tiles, K blocks per tile
+    int neg_base;               // some base_exp < 0: decode mode 1
     uint32_t tmem_cols;
 };
+
+struct GemmMaps { CUtensorMap sm[kMaxGemmTensors]; CUtensorMap gr[kMaxGemmTensors]; };
+
+struct TileRef { int ti; int mt; };      // tensor and row tile inside it
+__device__ __forceinline__ TileRef locate_mtile(const GemmParams& P, int mtg)
+{
+    int ti = 0;
+    while (ti + 1 < P.nt && mtg >= P.t[ti].mtile_end) ti++;
+    return TileRef{ti, mtg - (ti ? P.t[ti - 1].mtile_end : 0)};
+}
 
 // ----------------------------------------------------------------------------
 // tcgen05 / TMA wrappers
@@ -153,7 +172,7 @@ __host__ __device__ __forceinline__ Range cta_range(long long T, int G, int cta)
 // One decode thread owns one (row, 16-column chunk) of every K block.
 template <int kMode>
 __device__ __forceinline__ void decode_item(const uint8_t* raw, uint8_t* A, int item, uint32_t off_lo, uint32_t off_hi,
-                                            uint32_t base2, const GemmParams& P, int m0, int k0)
+                                            uint32_t base2, const GemmTensor& P, int m0, int k0)
 {
     const uint4 s = *reinterpret_cast<const uint4*>(raw + item * 16);
     const uint2 g = *reinterpret_cast<const uint2*>(raw + kTileRows * kTK + item * 8);
@@ -188,8 +207,8 @@ __device__ __forceinline__ void decode_item(const uint8_t* raw, uint8_t* A, int 
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant__ CUtensorMap map_gr,
-               const __grid_constant__ CUtensorMap map_x, const __grid_constant__ GemmParams P)
+gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CUtensorMap map_x,
+               const __grid_constant__ GemmParams P)
 {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     // swizzled operand tiles need 1024-byte alignment
@@ -237,16 +256,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
         // weights are never written, so this loop does not wait for the predecessor kernel
         if (lane == 0) {
             int sr = 0, tile = tile0, kb = kb0;
-            int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+            int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
+            TileRef tr = locate_mtile(P, mtg);
             uint32_t wr = 0;
             for (int it = rg.lo; it < rg.hi; it++) {
                 if (wr > 0) mbar_wait(b_rawempty + 8 * sr, (wr - 1) & 1, P.status, 0x10u, &s_abort);
                 mbar_arrive_expect_tx(b_rawfull + 8 * sr, kRawBytes);
                 const uint32_t rdst = smem_addr(raw + sr * kRawBytes);
-                tma_load_2d(rdst, &map_sm, kb * kTK, mt * kTileRows, b_rawfull + 8 * sr);
-                tma_load_2d(rdst + kTileRows * kTK, &map_gr, kb * (kTK / 2), mt * kTileRows, b_rawfull + 8 * sr);
+                tma_load_2d(rdst, &maps.sm[tr.ti], kb * kTK, tr.mt * kTileRows, b_rawfull + 8 * sr);
+                tma_load_2d(rdst + kTileRows * kTK, &maps.gr[tr.ti], kb * (kTK / 2), tr.mt * kTileRows, b_rawfull + 8 * sr);
                 if (++sr == kRawStages) { sr = 0; wr++; }
-                if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mt++; } }
+                if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mtg++; tr = locate_mtile(P, mtg); } }
             }
         }
     } else if (warp == 2) {
@@ -316,7 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
         int sr = gi % kRawStages, tile = tile0, kb = kb0 + gi;
         uint32_t wr = gi / kRawStages, wo = 0;
         while (kb >= KB) { kb -= KB; tile++; }
-        int mt = tile / P.n_ntiles;
+        TileRef tr = locate_mtile(P, tile / P.n_ntiles);
         uint8_t* Ap = Abuf + gi * kABytes;
         for (int it = rg.lo + gi; it < rg.hi; it += kDecodeGroups) {
             mbar_wait(b_rawfull + 8 * sr, wr & 1, P.status, 0x200u, &s_abort);
@@ -326,8 +346,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
             for (int j = 0; j < kItemsPerThread; j++) {
                 const int item = t + j * kGroupThreads;
                 const uint32_t o2 = j * (kGroupThreads / 4) * 128;
-                if (P.neg_base) decode_item<1>(rawp, Ap, item, off_lo + o2, off_hi + o2, P.base2, P, mt * kTileRows, kb * kTK);
-                else decode_item<0>(rawp, Ap, item, off_lo + o2, off_hi + o2, P.base2, P, mt * kTileRows, kb * kTK);
+                const GemmTensor& T = P.t[tr.ti];
+                if (P.neg_base) decode_item<1>(rawp, Ap, item, off_lo + o2, off_hi + o2, T.base2, T, tr.mt * kTileRows, kb * kTK);
+                else decode_item<0>(rawp, Ap, item, off_lo + o2, off_hi + o2, T.base2, T, tr.mt * kTileRows, kb * kTK);
             }
             fence_async_smem();                                   // generic-proxy writes -> visible to the MMA
             __syncwarp();
@@ -338,7 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
             kb += kDecodeGroups;
             if (kb >= KB) {
                 while (kb >= KB) { kb -= KB; tile++; }
-                mt = tile / P.n_ntiles;
+                tr = locate_mtile(P, tile / P.n_ntiles);
             }
         }
     } else if (warp >= kFirstEpiWarp) {
@@ -351,7 +372,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
             const int tile_lo = tile * KB, tile_end = tile_lo + KB;
             const int seg_end = tile_end < rg.hi ? tile_end : rg.hi;
             const bool whole = it == tile_lo && seg_end == tile_end;
-            const int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+            const int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
+            const TileRef tr = locate_mtile(P, mtg);
+            const GemmTensor& T = P.t[tr.ti];
+            const int mt = tr.mt;
             const int buf = two_acc ? (nacc & 1) : 0;
             const int uses = two_acc ? (nacc >> 1) : nacc;
             mbar_wait(b_accfull + 8 * buf, uses & 1, P.status, 0x800u, &s_abort);
@@ -369,10 +393,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_sm, const __grid_constant
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kHalves * BN + h * BN + c0), v);
                 tmem_ld_wait();
                 if (whole) {
-                    if (m < P.M) {
+                    if (m < T.M) {
 #pragma unroll
                         for (int j = 0; j < 32; j++)
-                            if (b0 + c0 + j < P.B) P.out[(size_t)(b0 + c0 + j) * P.out_stride + m] = __uint_as_float(v[j]);
+                            if (b0 + c0 + j < P.B) T.out[(size_t)(b0 + c0 + j) * T.out_stride + m] = __uint_as_float(v[j]);
                     }
                 } else {
 #pragma unroll
@@ -412,7 +436,10 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
     int c_last = c_first;
     while (c_last + 1 < G && cta_range(T, G, c_last + 1).lo < tile_end) c_last++;
     if (c_first == c_last) return;
-    const int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+    const int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
+    const TileRef tr = locate_mtile(P, mtg);
+    const GemmTensor& W = P.t[tr.ti];
+    const int mt = tr.mt;
     constexpr int kRowLanes = kTileRows / 4;                     // threads across the rows of a tile
     const int m4 = (threadIdx.x % kRowLanes) * 4;                // four consecutive rows per thread
     const int b0 = nt * BN;
@@ -426,14 +453,14 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         const int m = mt * kTileRows + m4;
-        float* dst = P.out + (size_t)(b0 + j) * P.out_stride + m;
-        if (m + 3 < P.M && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        float* dst = W.out + (size_t)(b0 + j) * W.out_stride + m;
+        if (m + 3 < W.M && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
             *reinterpret_cast<float4*>(dst) = acc;
         } else {
-            if (m < P.M) dst[0] = acc.x;
-            if (m + 1 < P.M) dst[1] = acc.y;
-            if (m + 2 < P.M) dst[2] = acc.z;
-            if (m + 3 < P.M) dst[3] = acc.w;
+            if (m < W.M) dst[0] = acc.x;
+            if (m + 1 < W.M) dst[1] = acc.y;
+            if (m + 2 < W.M) dst[2] = acc.z;
+            if (m + 3 < W.M) dst[3] = acc.w;
         }
     }
 }
@@ -513,34 +540,55 @@ int gemm_tc_supported(const S12Tensor* w, int act_stride, int out_stride, int B)
     return encode_fn() != nullptr;
 }
 
-int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
-                   int B, void* stream, const char* who)
+// Fills the per-tensor part of the parameters and the tensor maps of up to four
+// tensors that share K and the activations.  Shared by every launch path.
+static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Tensor* w, int nt, const void* act,
+                     int act_stride, void* const* outs, const int* out_strides, int B, const char* who)
 {
-    if (reinterpret_cast<uintptr_t>(act) % 16) return fail(S12_ERR_UNSUPPORTED, "%s: activations must be 16-byte aligned", who);
-    GemmParams P = {};
-    const bool csr = w->row_off && w->cols && w->correct;
-    P.row_off = csr ? w->row_off : nullptr; P.cols = w->cols; P.correct = w->correct;
-    P.out = (float*)out; P.M = w->M; P.K = w->K; P.B = B; P.out_stride = out_stride;
+    P.nt = nt; P.K = w[0].K; P.B = B;
     P.BN = B >= 256 ? 256 : ((B + 15) / 16) * 16;
     if (P.BN < 32) P.BN = 32;
-    P.n_mtiles = (w->M + kTileRows - 1) / kTileRows;
     P.n_ntiles = (B + P.BN - 1) / P.BN;
-    P.KB = (w->K + kTK - 1) / kTK;
-    P.base2 = make_base2(w->base_exp);
-    P.neg_base = w->base_exp < 0;
+    P.KB = (P.K + kTK - 1) / kTK;
+    P.neg_base = 0;
+    int mtiles = 0;
+    for (int i = 0; i < nt; i++) {
+        const S12Tensor& s = w[i];
+        GemmTensor& t = P.t[i];
+        const bool csr = s.row_off && s.cols && s.correct;
+        t.row_off = csr ? s.row_off : nullptr; t.cols = s.cols; t.correct = s.correct;
+        t.out = (float*)outs[i]; t.M = s.M; t.out_stride = out_strides[i];
+        t.base2 = make_base2(s.base_exp);
+        P.neg_base |= s.base_exp < 0;
+        mtiles += (s.M + kTileRows - 1) / kTileRows;
+        t.mtile_end = mtiles;
+        if (!make_map(&maps.sm[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, s.sm, (uint64_t)s.K, (uint64_t)s.M, (uint64_t)s.K,
+                      kTK, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+            !make_map(&maps.gr[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, s.gr, (uint64_t)s.K / 2, (uint64_t)s.M, (uint64_t)s.K / 2,
+                      kTK / 2, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
+    }
+    for (int i = nt; i < kMaxGemmTensors; i++) { maps.sm[i] = maps.sm[0]; maps.gr[i] = maps.gr[0]; }
+    P.n_mtiles = mtiles;
+    if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)P.K, (uint64_t)B, (uint64_t)act_stride * 2,
+                  kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
     uint32_t cols = 32;
     while (cols < (uint32_t)(2 * kHalves * P.BN) && cols < 512) cols <<= 1;
     P.tmem_cols = cols;
-    P.status = device_status_word();
+    return S12_OK;
+}
 
-    CUtensorMap msm, mgr, mx;
-    if (!make_map(&msm, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->sm, (uint64_t)w->K, (uint64_t)w->M, (uint64_t)w->K,
-                  kTK, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_map(&mgr, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->gr, (uint64_t)w->K / 2, (uint64_t)w->M, (uint64_t)w->K / 2,
-                  kTK / 2, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)w->K, (uint64_t)B, (uint64_t)act_stride * 2,
-                  kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
-        return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
+int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_stride, void* const* outs,
+                         const int* out_strides, int B, void* stream, const char* who)
+{
+    if (reinterpret_cast<uintptr_t>(act) % 16) return fail(S12_ERR_UNSUPPORTED, "%s: activations must be 16-byte aligned", who);
+    GemmParams P = {};
+    GemmMaps maps;
+    CUtensorMap mx;
+    int rc = gemm_fill(P, maps, mx, w, nt, act, act_stride, outs, out_strides, B, who);
+    if (rc) return rc;
+    P.status = device_status_word();
 
     const long long T = (long long)P.n_mtiles * P.n_ntiles * P.KB;
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: problem too large for the tile schedule", who);
@@ -551,7 +599,7 @@ int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* ou
     if (T / grid < min_iters) grid = (int)((T + min_iters - 1) / min_iters);
     if (grid < 1) grid = 1;
     Scratch sc;
-    int rc = get_scratch((size_t)sms * 2 * 256 * kTileRows * sizeof(float), sc, who);   // sized for the largest launch
+    rc = get_scratch((size_t)sms * 2 * 256 * kTileRows * sizeof(float), sc, who);   // sized for the largest launch
     if (rc) return rc;
     P.ws = sc.ws;
     // does any tile have its K range shared between CTAs?
@@ -572,9 +620,17 @@ int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* ou
         if (rc) return rc;
         attr_set[dev] = true;
     }
-    rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, msm, mgr, mx, P);
+    rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, maps, mx, P);
     if (rc || !partial) return rc;
     return launch(gemm_reduce_kernel, dim3(P.n_mtiles * P.n_ntiles, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
+}
+
+int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
+                   int B, void* stream, const char* who)
+{
+    void* outs[1] = {out};
+    int strides[1] = {out_stride};
+    return gemm_tc_launch_multi(w, 1, act, act_stride, outs, strides, B, stream, who);
 }
 
 }  // namespace s12
@@ -658,32 +714,16 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     if (rc) return rc;
 
     GemmParams P = {};
-    const bool csr = w->row_off && w->cols && w->correct;
-    P.row_off = csr ? w->row_off : nullptr; P.cols = w->cols; P.correct = w->correct;
-    P.out = (float*)out; P.M = w->M; P.K = w->K; P.B = B; P.out_stride = out_stride;
-    P.BN = ((B + 15) / 16) * 16;
-    if (P.BN < 32) P.BN = 32;
-    P.n_mtiles = (w->M + kTileRows - 1) / kTileRows;
-    P.n_ntiles = 1;
-    P.KB = (w->K + kTK - 1) / kTK;
-    P.base2 = make_base2(w->base_exp);
-    P.neg_base = w->base_exp < 0;
-    uint32_t cols = 32;
-    while (cols < (uint32_t)(2 * kHalves * P.BN) && cols < 512) cols <<= 1;
-    P.tmem_cols = cols;
+    GemmMaps maps;
+    CUtensorMap mx;
+    void* outs[1] = {out};
+    int strides[1] = {out_stride};
+    rc = gemm_fill(P, maps, mx, w, 1, act, act_stride, outs, strides, B, who);
+    if (rc) return rc;
     P.status = st.status;
     P.ws = st.ws;
-
     const long long T = (long long)P.n_mtiles * P.KB;
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: M*K exceeds the tile schedule's range", who);
-    CUtensorMap msm, mgr, mx;
-    if (!make_map(&msm, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->sm, (uint64_t)w->K, (uint64_t)w->M, (uint64_t)w->K,
-                  kTK, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_map(&mgr, CU_TENSOR_MAP_DATA_TYPE_UINT8, w->gr, (uint64_t)w->K / 2, (uint64_t)w->M, (uint64_t)w->K / 2,
-                  kTK / 2, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)w->K, (uint64_t)B, (uint64_t)act_stride * 2,
-                  kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
-        return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
 
     // CTAs: as the regular path, then capped so that two partial tiles per CTA fit the fixed scratch
     const int sms = sm_count();
@@ -697,7 +737,7 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(T, grid, c).hi % P.KB != 0;
 
     const size_t smem = gemm_smem_bytes(P.BN);
-    rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, msm, mgr, mx, P);
+    rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, maps, mx, P);
     if (rc || !partial) return rc;
     return launch(gemm_reduce_kernel, dim3(P.n_mtiles, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
 }

@@ -283,6 +283,16 @@ class Split12Engine:
         check(self.lib.s12_gemm_async(C.byref(t), _ptr(bf16_in), act_stride, _ptr(out), out_stride, bs,
                                       _stream(stream)), "s12_gemm_async")
 
+    def gemm_multi(self, ws: Sequence[CompressedWeight], bf16_in: torch.Tensor, outs: Sequence[torch.Tensor],
+                   act_stride: int, bs: int, stream=None, exact: bool = True) -> None:
+        """Up to four tensors sharing the activations (q/k/v, gate/up) as one tensor-core launch."""
+        n = len(ws)
+        arr = (S12Tensor * n)(*[w.tensor(with_csr=exact) for w in ws])
+        optr = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+        strides = (C.c_int * n)(*[o.stride(0) for o in outs])
+        check(self.lib.s12_gemm_multi_async(arr, n, _ptr(bf16_in), act_stride, optr, strides, bs, _stream(stream)),
+              "s12_gemm_multi_async")
+
     def gemm_noalloc(self, w: CompressedWeight, bf16_in: torch.Tensor, out: torch.Tensor, act_stride: int,
                      out_stride: int, bs: int, stream=None, exact: bool = True) -> None:
         """s12_gemm_async for callers that may not allocate: scratch is a fixed array in the library."""
