@@ -51,10 +51,21 @@ constexpr int kTK = 64;                  // columns per K block
 // Three independent rings.  Raw packed tiles come from HBM (about a microsecond
 // away) and are small, so that ring is deep; activation tiles come from L2;
 // decoded A tiles are produced and consumed inside the SM.
-constexpr int kRawStages = kHalves == 1 ? 5 : 3;
+// kATmem: the decoded A operand goes from registers straight into tensor memory
+// (tcgen05.st) and the MMA reads it from there, instead of through a swizzled
+// shared-memory tile.  Shared memory is the busiest resource of this kernel
+// (operand reads of the MMA, TMA writes, decode reads): this removes the A
+// tile's write and read (a quarter of the traffic), the swizzled stores and the
+// generic->async proxy fence.  Needs kHalves == 1.
+constexpr bool kATmem = true;
+constexpr int kRawStages = kATmem ? 7 : (kHalves == 1 ? 5 : 3);
 constexpr int kDecodeGroups = 4;         // decode warp groups; each owns one decoded-A stage
 constexpr int kAStages = kDecodeGroups;
-constexpr int kXStages = kHalves == 1 ? 3 : 2;
+constexpr int kXStages = kATmem ? 4 : (kHalves == 1 ? 3 : 2);
+constexpr int kASmemBytes = kATmem ? 0 : kAStages * kTileRows * kTK * 2;      // decoded A tiles in shared memory
+constexpr uint32_t kATmemCols = kTK / 2;                                     // 32-bit columns of one A stage in TMEM
+constexpr uint32_t kATmemBase = 512 - kAStages * kATmemCols;                 // A stages sit at the top of TMEM
+static_assert(!kATmem || kHalves == 1, "TMEM A operand: one 128-row MMA block per tile");
 constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2 * kXStages + 4;
 constexpr int kRawBytes = kTileRows * kTK + kTileRows * kTK / 2;   // 24576
 constexpr int kABytes = kTileRows * kTK * 2;                       // 32768
@@ -134,6 +145,26 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// same with the A operand in tensor memory (lane = row, one 32-bit column = two consecutive k)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
 {
@@ -206,6 +237,55 @@ __device__ __forceinline__ void decode_item(const uint8_t* raw, uint8_t* A, int 
     }
 }
 
+// Exact value of the escape at (row, col) from the CSR list, or -1 when the list
+// has no entry there.  Rare path, kept out of line.
+__device__ __noinline__ int find_escape(const GemmTensor& T, int row, int col)
+{
+    int a = T.row_off[row], hi0 = T.row_off[row + 1], b = hi0;
+    while (a < b) { int mid = (a + b) >> 1; if (T.cols[mid] < col) a = mid + 1; else b = mid; }
+    return (a < hi0 && T.cols[a] == col) ? (int)(uint16_t)T.correct[a] : -1;
+}
+
+// TMEM-A path: whole row of one K block.  Raw tiles are swizzled by TMA: sm rows
+// of 64 B with SWIZZLE_64B (16-byte chunk j of row r sits at chunk j ^ ((r>>1)&3)),
+// gr rows of 32 B with SWIZZLE_32B (chunk j at j ^ ((r>>2)&1)).  With a CSR
+// list (T.row_off != null) every group-0 element is replaced by its exact value.
+template <int kMode>
+__device__ __forceinline__ void decode_row(const uint8_t* raw, int r, const GemmTensor& T, int row, int k0,
+                                           uint32_t (&v)[32])
+{
+    const uint8_t* srow = raw + r * kTK;
+    const uint8_t* grow = raw + kTileRows * kTK + r * (kTK / 2);
+    const int ssw = (r >> 1) & 3, gsw = (r >> 2) & 1;
+    const uint32_t base2 = T.base2;
+    const bool patch = T.row_off != nullptr && row < T.M;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {                                // 16 columns per chunk
+        const uint4 s = *reinterpret_cast<const uint4*>(srow + ((c ^ ssw) << 4));
+        const uint2 g = *reinterpret_cast<const uint2*>(grow + (((c >> 1) ^ gsw) << 4) + (c & 1) * 8);
+        uint32_t p[4];
+        decode8<kMode>(s.x, s.y, g.x, base2, p);
+        v[8 * c + 0] = prmt(p[0], p[1], 0x5410u); v[8 * c + 1] = prmt(p[2], p[3], 0x5410u);
+        v[8 * c + 2] = prmt(p[0], p[1], 0x7632u); v[8 * c + 3] = prmt(p[2], p[3], 0x7632u);
+        decode8<kMode>(s.z, s.w, g.y, base2, p);
+        v[8 * c + 4] = prmt(p[0], p[1], 0x5410u); v[8 * c + 5] = prmt(p[2], p[3], 0x5410u);
+        v[8 * c + 6] = prmt(p[0], p[1], 0x7632u); v[8 * c + 7] = prmt(p[2], p[3], 0x7632u);
+        if (patch && (zero_nibbles(g.x) | zero_nibbles(g.y))) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const uint32_t gw = i < 8 ? g.x : g.y;
+                if (((gw >> (4 * (i & 7))) & 0xFu) == 0u) {
+                    const int val = find_escape(T, row, k0 + c * 16 + i);
+                    if (val >= 0) {
+                        uint32_t& dst = v[8 * c + (i >> 1)];
+                        dst = (i & 1) ? ((dst & 0x0000FFFFu) | ((uint32_t)val << 16)) : ((dst & 0xFFFF0000u) | (uint32_t)val);
+                    }
+                }
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CUtensorMap map_x,
                const __grid_constant__ GemmParams P)
@@ -217,7 +297,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     const uint32_t xbytes = (uint32_t)BN * 128u;
     uint8_t* raw = smem;                                         // [kRawStages][24576]
     uint8_t* Abuf = raw + kRawStages * kRawBytes;                // [kAStages][kHalves x 16384]
-    uint8_t* Xbuf = Abuf + kAStages * kABytes;                   // [kXStages][BN*128]
+    uint8_t* Xbuf = Abuf + kASmemBytes;                          // [kXStages][BN*128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(Xbuf + (size_t)kXStages * xbytes);
     const uint32_t b_rawfull = smem_addr(bars);                  // [kRawStages]
     const uint32_t b_rawempty = b_rawfull + 8 * kRawStages;      // [kRawStages]
@@ -249,7 +329,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     const int KB = P.KB;
     const Range rg = cta_range((long long)P.n_mtiles * P.n_ntiles * KB, gridDim.x, blockIdx.x);
     const int tile0 = rg.lo / KB, kb0 = rg.lo - tile0 * KB;     // the only divisions of the schedule
-    const bool two_acc = 2 * kHalves * BN <= (int)P.tmem_cols;   // accumulators are double buffered
+    const bool two_acc = 2 * kHalves * BN <= (int)(kATmem ? kATmemBase : P.tmem_cols);   // accumulators double buffered
 
     if (warp == 0) {
         // ------------------------------ raw-tile producer ---------------------
@@ -303,13 +383,21 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
                     mbar_wait(b_xfull + 8 * sx, wx & 1, P.status, 0x100u, &s_abort);
                     tc_fence_after();
                     const uint64_t bd = smem_desc_sw128(smem_addr(Xbuf + (size_t)sx * xbytes));
+                    if (kATmem) {
+                        const uint32_t a_tmem = tmem_base + kATmemBase + (uint32_t)sa * kATmemCols;
 #pragma unroll
-                    for (int h = 0; h < kHalves; h++) {
-                        const uint64_t ad = smem_desc_sw128(smem_addr(Abuf + sa * kABytes + h * (kTM * kTK * 2)));
+                        for (int k = 0; k < kTK / 16; k++)       // 16 k = 8 columns of packed bf16 pairs
+                            umma_bf16_ts(d_tmem, a_tmem + (uint32_t)(8 * k), bd + (uint64_t)(2 * k), idesc,
+                                         k == 0 ? accumulate : 1u);
+                    } else {
 #pragma unroll
-                        for (int k = 0; k < kTK / 16; k++)
-                            umma_bf16(d_tmem + (uint32_t)(h * BN), ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc,
-                                      k == 0 ? accumulate : 1u);
+                        for (int h = 0; h < kHalves; h++) {
+                            const uint64_t ad = smem_desc_sw128(smem_addr(Abuf + sa * kABytes + h * (kTM * kTK * 2)));
+#pragma unroll
+                            for (int k = 0; k < kTK / 16; k++)
+                                umma_bf16(d_tmem + (uint32_t)(h * BN), ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc,
+                                          k == 0 ? accumulate : 1u);
+                        }
                     }
                     accumulate = 1;
                     umma_commit(b_afree + 8 * sa);               // both stages are free when these MMAs finish
@@ -342,6 +430,20 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             mbar_wait(b_rawfull + 8 * sr, wr & 1, P.status, 0x200u, &s_abort);
             if (wo > 0) mbar_wait(b_afree + 8 * gi, (wo - 1) & 1, P.status, 0x400u, &s_abort);
             const uint8_t* rawp = raw + sr * kRawBytes;
+            if (kATmem) {
+                // thread t of the group owns row t of the tile: its 64 sm bytes and 32 gr bytes of this K
+                // block (the raw tiles are TMA-swizzled so that 32 rows read without bank conflicts),
+                // decoded to 32 registers of bf16 pairs in k order = 32 TMEM columns of lane t
+                const GemmTensor& T = P.t[tr.ti];
+                uint32_t v[32];
+                if (P.neg_base) decode_row<1>(rawp, t, T, tr.mt * kTileRows + t, kb * kTK, v);
+                else decode_row<0>(rawp, t, T, tr.mt * kTileRows + t, kb * kTK, v);
+                tmem_st32(tmem_base + ((uint32_t)((t >> 5) * 32) << 16) + kATmemBase + (uint32_t)gi * kATmemCols, v);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(b_afull + 8 * gi); mbar_arrive(b_rawempty + 8 * sr); }
+            } else {
 #pragma unroll
             for (int j = 0; j < kItemsPerThread; j++) {
                 const int item = t + j * kGroupThreads;
@@ -353,6 +455,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             fence_async_smem();                                   // generic-proxy writes -> visible to the MMA
             __syncwarp();
             if (lane == 0) { mbar_arrive(b_afull + 8 * gi); mbar_arrive(b_rawempty + 8 * sr); }
+            }
             sr += kDecodeGroups;
             while (sr >= kRawStages) { sr -= kRawStages; wr++; }
             wo++;
@@ -470,7 +573,7 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
 // ----------------------------------------------------------------------------
 static size_t gemm_smem_bytes(int BN)
 {
-    return (size_t)kRawStages * kRawBytes + (size_t)kAStages * kABytes + (size_t)kXStages * BN * 128 +
+    return (size_t)kRawStages * kRawBytes + (size_t)kASmemBytes + (size_t)kXStages * BN * 128 +
            8 * kNumBars + 16 + 1024;
 }
 
@@ -563,9 +666,9 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
         mtiles += (s.M + kTileRows - 1) / kTileRows;
         t.mtile_end = mtiles;
         if (!make_map(&maps.sm[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, s.sm, (uint64_t)s.K, (uint64_t)s.M, (uint64_t)s.K,
-                      kTK, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                      kTK, kTileRows, kATmem ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE) ||
             !make_map(&maps.gr[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, s.gr, (uint64_t)s.K / 2, (uint64_t)s.M, (uint64_t)s.K / 2,
-                      kTK / 2, kTileRows, CU_TENSOR_MAP_SWIZZLE_NONE))
+                      kTK / 2, kTileRows, kATmem ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE))
             return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
     }
     for (int i = nt; i < kMaxGemmTensors; i++) { maps.sm[i] = maps.sm[0]; maps.gr[i] = maps.gr[0]; }
@@ -575,7 +678,7 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
         return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
     uint32_t cols = 32;
     while (cols < (uint32_t)(2 * kHalves * P.BN) && cols < 512) cols <<= 1;
-    P.tmem_cols = cols;
+    P.tmem_cols = kATmem ? 512u : cols;
     return S12_OK;
 }
 
