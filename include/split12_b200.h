@@ -205,7 +205,7 @@ int s12_gemm_multi_async(const S12Tensor* w, int num_tensors, const void* act, i
  * number of CTAs is reduced until their partials fit, so large problems run
  * slower than through s12_gemm_async.  The call never calls cudaMalloc, cudaFree
  * or any allocating library routine.  Limits: B > 256 is refused with
- * S12_ERR_TOO_LARGE; B <= 16, K < 64, K % 32 != 0 or unaligned pointers with
+ * S12_ERR_TOO_LARGE; B <= 16, K < 256, K % 32 != 0 or unaligned pointers with
  * S12_ERR_UNSUPPORTED.  The first call on each device looks up the array's
  * device address (cudaGetSymbolAddress) and sets a kernel attribute; make that
  * first call before any stream capture.  All calls on a device share the one

@@ -130,6 +130,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity), "r"(kWaitHintNs) : "memory");
     return ok != 0;
 }
+// Non-blocking test of a phase: true when the phase with this parity has completed.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Returns false when the wait gave up: `site` is then ORed into *status and
 // *cta_abort (shared memory) is raised, which makes every later wait of the CTA
 // give up after a single poll, so a lost signal costs seconds, not hours.

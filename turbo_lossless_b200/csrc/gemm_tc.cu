@@ -4,26 +4,25 @@
 //   C[b, m] = sum_k W[m, k] * X[b, k]      fp32 out[b*out_stride + m]
 //
 // Roles inside one persistent CTA (one CTA per SM, 24 warps).  A CTA tile is
-// kTileRows weight rows x BN sequences (kHalves 128-row MMA blocks sharing one
-// activation tile).
-//   warp 0       raw-tile producer: TMA tensor-map loads of the packed tile
-//                (rows x 64 sm bytes, rows x 32 gr bytes) into a deep ring;
-//                runs ahead of everything else, weights come from HBM
+// 128 weight rows x BN sequences.
+//   warp 0       raw-tile producer: per 256 weight columns three TMA tensor-map
+//                loads (two 128 B x 128-row sm boxes, one 128 B x 128-row gr box,
+//                128-byte swizzle) into a two-stage ring; weights come from HBM
 //   warp 2       activation producer: TMA loads of the activation tile
 //                (BN sequences x 64 k, 128-byte swizzle) into its own ring
 //   warp 1       owns tensor memory (alloc/dealloc) and issues the MMAs from
-//                one thread: per 64-column block kHalves x 4 tcgen05.mma
-//                (M=128, N=BN, K=16, bf16 x bf16 -> fp32 in TMEM)
-//   warps 4-19   decode: raw bytes -> bf16 (decode8, escapes patched from the
-//                CSR list when the tensor brings one) written into the
-//                K-major, 128-byte-swizzled A tiles the MMA descriptor expects,
-//                then fence.proxy.async + mbarrier arrive
+//                one thread: per 64-column block 4 tcgen05.mma (M=128, N=BN,
+//                K=16, bf16 x bf16 -> fp32), A operand read from tensor memory
+//   warps 4-19   decode, four groups of 128 threads: thread t of group g turns
+//                row t, columns [64g, 64g+64) of the raw stage into bf16
+//                (decode8, escapes patched from the CSR list when the tensor
+//                brings one) and writes them with tcgen05.st into A stage g
 //   warps 20-23  epilogue: tcgen05.ld of the finished accumulators (double
-//                buffered in TMEM when 4*BN <= 512 columns), coalesced fp32
+//                buffered in TMEM when 2*BN <= 384 columns), coalesced fp32
 //                stores (32 consecutive m per store)
 //   warp 3       idle
 //
-// Work is split stream-K style: the (M tiles x N tiles x K blocks) iteration
+// Work is split stream-K style: the (M tiles x N tiles x 256-column blocks) iteration
 // space is cut into equal contiguous ranges, one per CTA, so a 4096-row
 // projection (32 tiles) still occupies all 148 SMs.  A CTA that covers only
 // part of a tile's K range writes its partial accumulator to a workspace and
@@ -44,37 +43,44 @@
 
 namespace s12 {
 
-constexpr int kTM = 128;                 // rows of one MMA (tcgen05 M)
-constexpr int kHalves = 1;               // MMA row blocks per CTA tile sharing one activation tile (1 or 2)
-constexpr int kTileRows = kTM * kHalves; // weight rows per CTA tile
-constexpr int kTK = 64;                  // columns per K block
-// Three independent rings.  Raw packed tiles come from HBM (about a microsecond
-// away) and are small, so that ring is deep; activation tiles come from L2;
-// decoded A tiles are produced and consumed inside the SM.
-// kATmem: the decoded A operand goes from registers straight into tensor memory
-// (tcgen05.st) and the MMA reads it from there, instead of through a swizzled
-// shared-memory tile.  Shared memory is the busiest resource of this kernel
-// (operand reads of the MMA, TMA writes, decode reads): this removes the A
-// tile's write and read (a quarter of the traffic), the swizzled stores and the
-// generic->async proxy fence.  Needs kHalves == 1.
-constexpr bool kATmem = true;
-constexpr int kRawStages = kATmem ? 7 : (kHalves == 1 ? 5 : 3);
-constexpr int kDecodeGroups = 4;         // decode warp groups; each owns one decoded-A stage
+constexpr int kTM = 128;                 // rows of one MMA (tcgen05 M) = weight rows per CTA tile
+constexpr int kTileRows = kTM;
+constexpr int kTK = 64;                  // columns of one MMA K block (one 128-byte swizzle atom of bf16)
+constexpr int kSub = 4;                  // K blocks per raw stage
+constexpr int kBigK = kTK * kSub;        // 256 columns of packed weights per raw stage
+// The TMA engine's cost is per box row (measured on this part: a 64 B x 128-row
+// box streams at 4.3 TB/s over 148 SMs, a 32 B one at 2.3 TB/s, 128 B at 6 TB/s),
+// and with 64-column raw boxes the kernel was bound by exactly that.  A raw
+// stage is therefore 256 columns wide: two 128 B x 128-row sm boxes and one
+// 128 B x 128-row gr box, all with the 128-byte swizzle so that a thread reading
+// its own row does not collide with the 31 other rows of its warp.
+constexpr int kRawBoxBytes = kTM * 128;                  // 16384
+constexpr int kRawBytes = 3 * kRawBoxBytes;              // 49152: sm[0:128], sm[128:256], gr
+constexpr int kRawStages = 2;
+constexpr int kXStages = kSub;           // activation stage s pairs with A stage s: both hold K block s of a raw stage
+constexpr int kDecodeGroups = kSub;      // group g decodes K block g of every raw stage into A stage g
 constexpr int kAStages = kDecodeGroups;
-constexpr int kXStages = kATmem ? 4 : (kHalves == 1 ? 3 : 2);
-constexpr int kASmemBytes = kATmem ? 0 : kAStages * kTileRows * kTK * 2;      // decoded A tiles in shared memory
+constexpr int kNumBars = 2 * kRawStages + 2 * kSub + 4;
 constexpr uint32_t kATmemCols = kTK / 2;                                     // 32-bit columns of one A stage in TMEM
 constexpr uint32_t kATmemBase = 512 - kAStages * kATmemCols;                 // A stages sit at the top of TMEM
-static_assert(!kATmem || kHalves == 1, "TMEM A operand: one 128-row MMA block per tile");
-constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2 * kXStages + 4;
-constexpr int kRawBytes = kTileRows * kTK + kTileRows * kTK / 2;   // 24576
-constexpr int kABytes = kTileRows * kTK * 2;                       // 32768
-constexpr int kDecodeWarps = 16;         // 512 threads: one (row, 16-column chunk) each per K block
+constexpr int kDecodeWarps = 16;         // 4 groups x 4 warps: thread t of a group owns row t of the tile
 constexpr int kFirstDecodeWarp = 4, kFirstEpiWarp = kFirstDecodeWarp + kDecodeWarps;
 constexpr int kGemmThreads = (kFirstEpiWarp + 4) * 32;
 constexpr int kGroupThreads = kDecodeWarps * 32 / kDecodeGroups;            // 128
-constexpr int kItemsPerThread = kTileRows * 4 / kGroupThreads;               // 4 when kTileRows == 128
-static_assert((kGroupThreads / 4) % 8 == 0, "row step must keep the swizzle phase");
+static_assert(kGroupThreads == kTM, "one decode thread per tile row");
+
+#ifdef S12_GEMM_TRACE
+// Development aid: cycle stamps of the pipeline roles of CTA 0, per raw stage.
+__device__ long long g_gtrace[64][48];
+#define GT(i, slot) do { if (blockIdx.x == 0 && (i) < 64) g_gtrace[(i)][(slot)] = clock64(); } while (0)
+// wall-clock (ns) stamps of kernel phases, per CTA; row 160 = reduce kernel (min start, max end)
+__device__ unsigned long long g_gphase[161][8];
+__device__ __forceinline__ unsigned long long gt_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define GP(slot) do { g_gphase[blockIdx.x][(slot)] = gt_now(); } while (0)
+#else
+#define GT(i, slot) do { } while (0)
+#define GP(slot) do { } while (0)
+#endif
 
 constexpr int kMaxGemmTensors = 4;       // tensors sharing K and the activations in one launch (q/k/v, gate/up)
 
@@ -200,91 +206,125 @@ __host__ __device__ __forceinline__ Range cta_range(long long T, int G, int cta)
     return Range{(int)(T * cta / G), (int)(T * (cta + 1) / G)};
 }
 
-// One decode thread owns one (row, 16-column chunk) of every K block.
-template <int kMode>
-__device__ __forceinline__ void decode_item(const uint8_t* raw, uint8_t* A, int item, uint32_t off_lo, uint32_t off_hi,
-                                            uint32_t base2, const GemmTensor& P, int m0, int k0)
+// Walks one row's CSR escape list in column order, two entries ahead of the
+// column range being decoded, so that the loads of an entry are long finished
+// when the entry is needed (a decode thread meets one every few raw stages).
+struct EscCursor {
+    int pos, end;               // index of the entry in c0/v0, end of the row's list
+    int c0, c1;                 // columns of the current and the next entry (INT_MAX: none)
+    uint32_t v0, v1;            // their exact bf16 bit patterns
+};
+constexpr int kNoEscape = 0x7FFFFFFF;
+// Positions the cursor on the first entry of `row` with column >= kstart.
+__device__ __noinline__ void esc_seek(EscCursor& e, const GemmTensor& T, int row, int kstart)
 {
-    const uint4 s = *reinterpret_cast<const uint4*>(raw + item * 16);
-    const uint2 g = *reinterpret_cast<const uint2*>(raw + kTileRows * kTK + item * 8);
-    uint32_t p[4], lo[4], hi[4];
-    decode8<kMode>(s.x, s.y, g.x, base2, p);
-    lo[0] = prmt(p[0], p[1], 0x5410u); lo[1] = prmt(p[2], p[3], 0x5410u);
-    lo[2] = prmt(p[0], p[1], 0x7632u); lo[3] = prmt(p[2], p[3], 0x7632u);
-    decode8<kMode>(s.z, s.w, g.y, base2, p);
-    hi[0] = prmt(p[0], p[1], 0x5410u); hi[1] = prmt(p[2], p[3], 0x5410u);
-    hi[2] = prmt(p[0], p[1], 0x7632u); hi[3] = prmt(p[2], p[3], 0x7632u);
-    *reinterpret_cast<uint4*>(A + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    *reinterpret_cast<uint4*>(A + off_hi) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-    if (P.row_off != nullptr && (zero_nibbles(g.x) | zero_nibbles(g.y))) {
-        const int r = item >> 2, c = item & 3, sw = r & 7;
-        const int row = m0 + r;
-        if (row < P.M) {
-            const int lo0 = P.row_off[row], hi0 = P.row_off[row + 1];
-#pragma unroll 1
-            for (int i = 0; i < 16; i++) {
-                const uint32_t gw = i < 8 ? g.x : g.y;
-                if (((gw >> (4 * (i & 7))) & 0xFu) != 0u) continue;
-                const int col = k0 + c * 16 + i;
-                int a = lo0, b = hi0;
-                while (a < b) { int mid = (a + b) >> 1; if (P.cols[mid] < col) a = mid + 1; else b = mid; }
-                if (a < hi0 && P.cols[a] == col) {
-                    const int kc = c * 16 + i;              // column inside the K block
-                    *reinterpret_cast<uint16_t*>(A + r * 128 + (((kc >> 3) ^ sw) << 4) + (kc & 7) * 2) = (uint16_t)P.correct[a];
-                }
-            }
+    e.pos = e.end = 0; e.c0 = e.c1 = kNoEscape; e.v0 = e.v1 = 0;
+    if (T.row_off == nullptr || row >= T.M) return;
+    int a = T.row_off[row], b = T.row_off[row + 1];
+    e.end = b;
+    while (a < b) { const int mid = (a + b) >> 1; if (T.cols[mid] < kstart) a = mid + 1; else b = mid; }
+    e.pos = a;
+    if (a < e.end) { e.c0 = T.cols[a]; e.v0 = (uint16_t)T.correct[a]; }
+    if (a + 1 < e.end) { e.c1 = T.cols[a + 1]; e.v1 = (uint16_t)T.correct[a + 1]; }
+}
+__device__ __forceinline__ void esc_advance(EscCursor& e, const GemmTensor& T)
+{
+    e.c0 = e.c1; e.v0 = e.v1; e.c1 = kNoEscape;
+    e.pos++;
+    if (e.pos + 1 < e.end) { e.c1 = T.cols[e.pos + 1]; e.v1 = (uint16_t)T.correct[e.pos + 1]; }
+}
+// Replaces the listed escapes of columns [k0, k0 + 64) in the decoded registers
+// (v[i] holds columns k0 + 2i and k0 + 2i + 1) and moves the cursor past k0 + 64.
+__device__ __forceinline__ void esc_apply(EscCursor& e, const GemmTensor& T, int k0, uint32_t (&v)[32])
+{
+    while (e.c0 < k0 + kTK) {
+        const int idx = e.c0 - k0;
+        if (idx >= 0) {
+            const uint32_t keep = (idx & 1) ? 0x0000FFFFu : 0xFFFF0000u, ins = (idx & 1) ? (e.v0 << 16) : e.v0;
+            // one predicated (v & keep) | ins per register: written as PTX so that the register array is
+            // not turned into an indexed local-memory array
+            const int h = idx >> 1;
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                asm("{\n\t.reg .pred p;\n\tsetp.eq.s32 p, %1, %2;\n\t@p lop3.b32 %0, %0, %3, %4, 0xEA;\n\t}"
+                    : "+r"(v[i]) : "r"(h), "r"(i), "r"(keep), "r"(ins));
         }
+        esc_advance(e, T);
     }
 }
 
-// Exact value of the escape at (row, col) from the CSR list, or -1 when the list
-// has no entry there.  Rare path, kept out of line.
-__device__ __noinline__ int find_escape(const GemmTensor& T, int row, int col)
+// One thread's share of a raw stage: row r, 64 columns of K block `sub` = 64 sm
+// bytes and 32 gr bytes.  The raw boxes carry the 128-byte swizzle: 16-byte
+// chunk j of row r sits at chunk j ^ (r & 7).
+struct RawRow { uint4 s[4]; uint4 g[2]; };
+__device__ __forceinline__ void load_raw_row(const uint8_t* raw, int r, int sub, RawRow& q)
 {
-    int a = T.row_off[row], hi0 = T.row_off[row + 1], b = hi0;
-    while (a < b) { int mid = (a + b) >> 1; if (T.cols[mid] < col) a = mid + 1; else b = mid; }
-    return (a < hi0 && T.cols[a] == col) ? (int)(uint16_t)T.correct[a] : -1;
+    const uint8_t* srow = raw + (sub >> 1) * kRawBoxBytes + r * 128;
+    const uint8_t* grow = raw + 2 * kRawBoxBytes + r * 128;
+    const int sw = r & 7, sc = (sub & 1) * 4, gc = sub * 2;
+#pragma unroll
+    for (int c = 0; c < 4; c++) q.s[c] = *reinterpret_cast<const uint4*>(srow + (((sc + c) ^ sw) << 4));
+#pragma unroll
+    for (int c = 0; c < 2; c++) q.g[c] = *reinterpret_cast<const uint4*>(grow + (((gc + c) ^ sw) << 4));
 }
 
-// TMEM-A path: whole row of one K block.  Raw tiles are swizzled by TMA: sm rows
-// of 64 B with SWIZZLE_64B (16-byte chunk j of row r sits at chunk j ^ ((r>>1)&3)),
-// gr rows of 32 B with SWIZZLE_32B (chunk j at j ^ ((r>>2)&1)).  With a CSR
-// list (T.row_off != null) every group-0 element is replaced by its exact value.
+// Decodes the 64 weights of a RawRow into 32 registers of bf16 pairs in k order
+// (= 32 TMEM columns of the thread's lane); escapes get the exponent base_exp.
 template <int kMode>
-__device__ __forceinline__ void decode_row(const uint8_t* raw, int r, const GemmTensor& T, int row, int k0,
-                                           uint32_t (&v)[32])
+__device__ __forceinline__ void decode_row(const RawRow& q, uint32_t base2, uint32_t (&v)[32])
 {
-    const uint8_t* srow = raw + r * kTK;
-    const uint8_t* grow = raw + kTileRows * kTK + r * (kTK / 2);
-    const int ssw = (r >> 1) & 3, gsw = (r >> 2) & 1;
-    const uint32_t base2 = T.base2;
-    const bool patch = T.row_off != nullptr && row < T.M;
 #pragma unroll
     for (int c = 0; c < 4; c++) {                                // 16 columns per chunk
-        const uint4 s = *reinterpret_cast<const uint4*>(srow + ((c ^ ssw) << 4));
-        const uint2 g = *reinterpret_cast<const uint2*>(grow + (((c >> 1) ^ gsw) << 4) + (c & 1) * 8);
+        const uint4 s = q.s[c];
+        const uint32_t gx = (c & 1) ? q.g[c >> 1].z : q.g[c >> 1].x, gy = (c & 1) ? q.g[c >> 1].w : q.g[c >> 1].y;
         uint32_t p[4];
-        decode8<kMode>(s.x, s.y, g.x, base2, p);
+        decode8<kMode>(s.x, s.y, gx, base2, p);
         v[8 * c + 0] = prmt(p[0], p[1], 0x5410u); v[8 * c + 1] = prmt(p[2], p[3], 0x5410u);
         v[8 * c + 2] = prmt(p[0], p[1], 0x7632u); v[8 * c + 3] = prmt(p[2], p[3], 0x7632u);
-        decode8<kMode>(s.z, s.w, g.y, base2, p);
+        decode8<kMode>(s.z, s.w, gy, base2, p);
         v[8 * c + 4] = prmt(p[0], p[1], 0x5410u); v[8 * c + 5] = prmt(p[2], p[3], 0x5410u);
         v[8 * c + 6] = prmt(p[0], p[1], 0x7632u); v[8 * c + 7] = prmt(p[2], p[3], 0x7632u);
-        if (patch && (zero_nibbles(g.x) | zero_nibbles(g.y))) {
+    }
+}
+
+// Moves 32-column chunks first, first+step, ... of a finished accumulator from
+// tensor memory to their destination: the output when the segment covered the
+// tile's whole K range, else this CTA's partial-tile slot of the workspace.
+// The calling thread owns accumulator row `mrow` (tensor-memory lane).
+__device__ __forceinline__ void drain_chunks(const GemmParams& P, const GemmTensor& T, uint32_t tmem_acc, int first, int step,
+                                             bool whole, int m, int mrow, int b0, float* wsp)
+{
+    const int BN = P.BN;
+    for (int c0 = first * 32; c0 < BN; c0 += step * 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_acc + (uint32_t)c0, v);
+        tmem_ld_wait();
+        if (whole) {
+            if (m < T.M) {
+                float* o = T.out + (size_t)(b0 + c0) * T.out_stride + m;
+                if (b0 + c0 + 32 <= P.B) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const uint32_t gw = i < 8 ? g.x : g.y;
-                if (((gw >> (4 * (i & 7))) & 0xFu) == 0u) {
-                    const int val = find_escape(T, row, k0 + c * 16 + i);
-                    if (val >= 0) {
-                        uint32_t& dst = v[8 * c + (i >> 1)];
-                        dst = (i & 1) ? ((dst & 0x0000FFFFu) | ((uint32_t)val << 16)) : ((dst & 0xFFFF0000u) | (uint32_t)val);
-                    }
+                    for (int j = 0; j < 32; j++) o[(size_t)j * T.out_stride] = __uint_as_float(v[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (b0 + c0 + j < P.B) o[(size_t)j * T.out_stride] = __uint_as_float(v[j]);
                 }
             }
+        } else {
+            float* o = wsp + (size_t)c0 * kTileRows + mrow;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (c0 + j < BN) o[j * kTileRows] = __uint_as_float(v[j]);
         }
     }
 }
+
+// When the accumulator cannot be double buffered (BN > 192) the MMAs of the next
+// tile wait for the drain, and so does everything upstream of them.  The decode
+// warps are then idle anyway and take part in the drain: per lane quarter the
+// epilogue warp and one warp of each decode group share the chunks.
+constexpr int kDrainTeams = 1 + kDecodeGroups;
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CUtensorMap map_x,
@@ -295,28 +335,28 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     uint8_t* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const int BN = P.BN;
     const uint32_t xbytes = (uint32_t)BN * 128u;
-    uint8_t* raw = smem;                                         // [kRawStages][24576]
-    uint8_t* Abuf = raw + kRawStages * kRawBytes;                // [kAStages][kHalves x 16384]
-    uint8_t* Xbuf = Abuf + kASmemBytes;                          // [kXStages][BN*128]
+    uint8_t* raw = smem;                                         // [kRawStages][kRawBytes]
+    uint8_t* Xbuf = raw + kRawStages * kRawBytes;                // [kXStages][BN*128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(Xbuf + (size_t)kXStages * xbytes);
     const uint32_t b_rawfull = smem_addr(bars);                  // [kRawStages]
     const uint32_t b_rawempty = b_rawfull + 8 * kRawStages;      // [kRawStages]
-    const uint32_t b_afull = b_rawempty + 8 * kRawStages;        // [kAStages]
-    const uint32_t b_afree = b_afull + 8 * kAStages;             // [kAStages]  MMA done with the A stage
-    const uint32_t b_xfull = b_afree + 8 * kAStages;             // [kXStages]
-    const uint32_t b_xfree = b_xfull + 8 * kXStages;             // [kXStages]  MMA done with the X stage
-    const uint32_t b_accfull = b_xfree + 8 * kXStages;           // [2]
+    // K block s of a raw stage has one pair of barriers for both of its operands: "full" counts the four
+    // decode warps' arrivals plus the activation tile's bytes, "free" is the MMA's commit
+    const uint32_t b_full = b_rawempty + 8 * kRawStages;         // [kSub]
+    const uint32_t b_free = b_full + 8 * kSub;                   // [kSub]
+    const uint32_t b_accfull = b_free + 8 * kSub;                // [2]
     const uint32_t b_accempty = b_accfull + 16;                  // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
 
     __shared__ int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool two_acc = 2 * BN <= (int)kATmemBase;              // accumulators double buffered
     if (threadIdx.x == 0) {
+        GP(0);
         s_abort = 0;
-        for (int i = 0; i < kRawStages; i++) { mbar_init(b_rawfull + 8 * i, 1); mbar_init(b_rawempty + 8 * i, kDecodeWarps / kDecodeGroups); }
-        for (int i = 0; i < kAStages; i++) { mbar_init(b_afull + 8 * i, kDecodeWarps / kDecodeGroups); mbar_init(b_afree + 8 * i, 1); }
-        for (int i = 0; i < kXStages; i++) { mbar_init(b_xfull + 8 * i, 1); mbar_init(b_xfree + 8 * i, 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(b_accfull + 8 * i, 1); mbar_init(b_accempty + 8 * i, 4); }
+        for (int i = 0; i < kRawStages; i++) { mbar_init(b_rawfull + 8 * i, 1); mbar_init(b_rawempty + 8 * i, kDecodeWarps); }
+        for (int i = 0; i < kSub; i++) { mbar_init(b_full + 8 * i, kDecodeWarps / kDecodeGroups + 1); mbar_init(b_free + 8 * i, 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(b_accfull + 8 * i, 1); mbar_init(b_accempty + 8 * i, two_acc ? 4 : 4 + kDecodeWarps); }
         mbar_fence_init();
     }
     if (warp == 1) { tmem_alloc(smem_addr(tmem_slot), P.tmem_cols); tmem_relinquish(); }
@@ -325,11 +365,13 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     grid_launch_dependents();
+    if (threadIdx.x == 0) GP(1);
 
+    // The schedule counts raw stages ("big blocks" of kBigK columns); a tile has
+    // KB of them, the last one zero-filled by TMA past column K.
     const int KB = P.KB;
     const Range rg = cta_range((long long)P.n_mtiles * P.n_ntiles * KB, gridDim.x, blockIdx.x);
     const int tile0 = rg.lo / KB, kb0 = rg.lo - tile0 * KB;     // the only divisions of the schedule
-    const bool two_acc = 2 * kHalves * BN <= (int)(kATmem ? kATmemBase : P.tmem_cols);   // accumulators double buffered
 
     if (warp == 0) {
         // ------------------------------ raw-tile producer ---------------------
@@ -341,10 +383,14 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             uint32_t wr = 0;
             for (int it = rg.lo; it < rg.hi; it++) {
                 if (wr > 0) mbar_wait(b_rawempty + 8 * sr, (wr - 1) & 1, P.status, 0x10u, &s_abort);
-                mbar_arrive_expect_tx(b_rawfull + 8 * sr, kRawBytes);
+                const uint32_t bar = b_rawfull + 8 * sr;
+                GT(it - rg.lo, 0);
+                mbar_arrive_expect_tx(bar, kRawBytes);
                 const uint32_t rdst = smem_addr(raw + sr * kRawBytes);
-                tma_load_2d(rdst, &maps.sm[tr.ti], kb * kTK, tr.mt * kTileRows, b_rawfull + 8 * sr);
-                tma_load_2d(rdst + kTileRows * kTK, &maps.gr[tr.ti], kb * (kTK / 2), tr.mt * kTileRows, b_rawfull + 8 * sr);
+                const int y = tr.mt * kTileRows;
+                tma_load_2d(rdst, &maps.sm[tr.ti], kb * kBigK, y, bar);
+                tma_load_2d(rdst + 2 * kRawBoxBytes, &maps.gr[tr.ti], kb * (kBigK / 2), y, bar);
+                tma_load_2d(rdst + kRawBoxBytes, &maps.sm[tr.ti], kb * kBigK + 128, y, bar);
                 if (++sr == kRawStages) { sr = 0; wr++; }
                 if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mtg++; tr = locate_mtile(P, mtg); } }
             }
@@ -353,116 +399,131 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
         // ------------------------------ activation-tile producer --------------
         if (lane == 0) {
             grid_dependency_wait();                              // activations come from the predecessor
-            int sx = 0, tile = tile0, kb = kb0;
+            int tile = tile0, kb = kb0;
             int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
-            uint32_t wx = 0;
             for (int it = rg.lo; it < rg.hi; it++) {
-                if (wx > 0) mbar_wait(b_xfree + 8 * sx, (wx - 1) & 1, P.status, 0x20u, &s_abort);
-                mbar_arrive_expect_tx(b_xfull + 8 * sx, xbytes);
-                tma_load_2d(smem_addr(Xbuf + (size_t)sx * xbytes), &map_x, kb * kTK, nt * BN, b_xfull + 8 * sx);
-                if (++sx == kXStages) { sx = 0; wx++; }
+#pragma unroll
+                for (int sub = 0; sub < kSub; sub++) {
+                    if (it > rg.lo) mbar_wait(b_free + 8 * sub, (uint32_t)(it - rg.lo - 1) & 1, P.status, 0x20u, &s_abort);
+                    GT(it - rg.lo, 1 + sub);
+                    mbar_arrive_expect_tx(b_full + 8 * sub, xbytes);
+                    tma_load_2d(smem_addr(Xbuf + (size_t)sub * xbytes), &map_x, kb * kBigK + sub * kTK, nt * BN, b_full + 8 * sub);
+                }
                 if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mt++; } }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ----------------------------
-        if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
-            int sa = 0, sx = 0, nacc = 0, it = rg.lo, tile_end = (tile0 + 1) * KB;
-            uint32_t wa = 0, wx = 0;
-            while (it < rg.hi) {
-                const int seg_end = tile_end < rg.hi ? tile_end : rg.hi;
-                const int buf = two_acc ? (nacc & 1) : 0;
-                const int uses = two_acc ? (nacc >> 1) : nacc;    // earlier uses of this accumulator
-                if (uses > 0) mbar_wait(b_accempty + 8 * buf, (uses - 1) & 1, P.status, 0x40u, &s_abort);
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kHalves * BN);
-                uint32_t accumulate = 0;
-                for (; it < seg_end; it++) {
-                    mbar_wait(b_afull + 8 * sa, wa & 1, P.status, 0x80u, &s_abort);
-                    mbar_wait(b_xfull + 8 * sx, wx & 1, P.status, 0x100u, &s_abort);
+        // The whole warp walks the schedule (uniform control flow, so that addresses and descriptors stay
+        // warp-uniform); lane 0 issues the MMAs and the commits.
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
+        const uint64_t bdesc0 = smem_desc_sw128(smem_addr(Xbuf));
+        const uint64_t bstep = (uint64_t)(xbytes >> 4);
+        int nacc = 0, it = rg.lo, tile_end = (tile0 + 1) * KB;
+        uint32_t wa = 0;
+        bool ready = false;                                       // the stage about to be used was seen full
+        while (it < rg.hi) {
+            const int seg_end = tile_end < rg.hi ? tile_end : rg.hi;
+            const int buf = two_acc ? (nacc & 1) : 0;
+            const int uses = two_acc ? (nacc >> 1) : nacc;        // earlier uses of this accumulator
+            if (uses > 0) mbar_wait(b_accempty + 8 * buf, (uses - 1) & 1, P.status, 0x40u, &s_abort);
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+            uint32_t accumulate = 0;
+            for (; it < seg_end; it++, wa++) {
+#pragma unroll
+                for (int sub = 0; sub < kSub; sub++) {
+                    if (!ready) mbar_wait(b_full + 8 * sub, wa & 1, P.status, 0x80u, &s_abort);
+                    GT(it - rg.lo, 5 + sub);
                     tc_fence_after();
-                    const uint64_t bd = smem_desc_sw128(smem_addr(Xbuf + (size_t)sx * xbytes));
-                    if (kATmem) {
-                        const uint32_t a_tmem = tmem_base + kATmemBase + (uint32_t)sa * kATmemCols;
+                    // look at the next stage now: the test's latency hides behind the MMA issue
+                    ready = sub + 1 < kSub ? mbar_test(b_full + 8 * (sub + 1), wa & 1) : mbar_test(b_full, (wa + 1) & 1);
+                    if (lane == 0) {
+                        const uint64_t bd = bdesc0 + (uint64_t)sub * bstep;
+                        const uint32_t a_tmem = tmem_base + kATmemBase + (uint32_t)sub * kATmemCols;
 #pragma unroll
                         for (int k = 0; k < kTK / 16; k++)       // 16 k = 8 columns of packed bf16 pairs
                             umma_bf16_ts(d_tmem, a_tmem + (uint32_t)(8 * k), bd + (uint64_t)(2 * k), idesc,
                                          k == 0 ? accumulate : 1u);
-                    } else {
-#pragma unroll
-                        for (int h = 0; h < kHalves; h++) {
-                            const uint64_t ad = smem_desc_sw128(smem_addr(Abuf + sa * kABytes + h * (kTM * kTK * 2)));
-#pragma unroll
-                            for (int k = 0; k < kTK / 16; k++)
-                                umma_bf16(d_tmem + (uint32_t)(h * BN), ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc,
-                                          k == 0 ? accumulate : 1u);
-                        }
+                        GT(it - rg.lo, 33 + sub);
+                        umma_commit(b_free + 8 * sub);           // A stage and activation stage are free when these finish
+                        GT(it - rg.lo, 37 + sub);
                     }
                     accumulate = 1;
-                    umma_commit(b_afree + 8 * sa);               // both stages are free when these MMAs finish
-                    umma_commit(b_xfree + 8 * sx);
-                    if (++sa == kAStages) { sa = 0; wa++; }
-                    if (++sx == kXStages) { sx = 0; wx++; }
                 }
-                umma_commit(b_accfull + 8 * buf);                // accumulator of this tile segment is complete
-                nacc++;
-                tile_end += KB;
             }
+            if (lane == 0) umma_commit(b_accfull + 8 * buf);     // accumulator of this tile segment is complete
+            __syncwarp();
+            nacc++;
+            tile_end += KB;
         }
     } else if (warp >= kFirstDecodeWarp && warp < kFirstEpiWarp) {
         // ------------------------------ decode --------------------------------
-        // kDecodeGroups groups of warps take K blocks in turn (group = block index
-        // mod kDecodeGroups) and each group owns one A stage, so a group has
-        // kDecodeGroups MMA periods for the wait -> load -> decode -> store ->
-        // fence -> arrive chain of its block, and a thread amortises that chain
-        // over kItemsPerThread (row, 16-column chunk) items.
+        // Group g (4 warps, thread t = tile row t) decodes K block g of every raw
+        // stage into A stage g of tensor memory, so the four groups work on the
+        // same raw stage side by side and each has a whole raw-stage period (four
+        // MMA periods) for its wait -> load -> decode -> tcgen05.st -> arrive chain.
         const int dt = threadIdx.x - kFirstDecodeWarp * 32;
         const int gi = dt / kGroupThreads, t = dt % kGroupThreads;
-        const int r = t >> 2, c = t & 3, sw = r & 7;              // row advances by kGroupThreads/4 per item, so r&7 is fixed
-        const uint32_t off_lo = r * 128 + (((2 * c) ^ sw) << 4), off_hi = r * 128 + (((2 * c + 1) ^ sw) << 4);
-        int sr = gi % kRawStages, tile = tile0, kb = kb0 + gi;
-        uint32_t wr = gi / kRawStages, wo = 0;
-        while (kb >= KB) { kb -= KB; tile++; }
+        int sr = 0, tile = tile0, kb = kb0;
+        int seg_kb0 = kb0, nacc = 0;                              // first K block and index of the current tile segment
+        uint32_t wr = 0, wo = 0;
         TileRef tr = locate_mtile(P, tile / P.n_ntiles);
-        uint8_t* Ap = Abuf + gi * kABytes;
-        for (int it = rg.lo + gi; it < rg.hi; it += kDecodeGroups) {
+        EscCursor esc;
+        esc_seek(esc, P.t[tr.ti], tr.mt * kTileRows + t, kb0 * kBigK + gi * kTK);
+        const uint32_t a_dst = tmem_base + ((uint32_t)((t >> 5) * 32) << 16) + kATmemBase + (uint32_t)gi * kATmemCols;
+        for (int it = rg.lo; it < rg.hi; it++) {
             mbar_wait(b_rawfull + 8 * sr, wr & 1, P.status, 0x200u, &s_abort);
-            if (wo > 0) mbar_wait(b_afree + 8 * gi, (wo - 1) & 1, P.status, 0x400u, &s_abort);
-            const uint8_t* rawp = raw + sr * kRawBytes;
-            if (kATmem) {
-                // thread t of the group owns row t of the tile: its 64 sm bytes and 32 gr bytes of this K
-                // block (the raw tiles are TMA-swizzled so that 32 rows read without bank conflicts),
-                // decoded to 32 registers of bf16 pairs in k order = 32 TMEM columns of lane t
-                const GemmTensor& T = P.t[tr.ti];
-                uint32_t v[32];
-                if (P.neg_base) decode_row<1>(rawp, t, T, tr.mt * kTileRows + t, kb * kTK, v);
-                else decode_row<0>(rawp, t, T, tr.mt * kTileRows + t, kb * kTK, v);
-                tmem_st32(tmem_base + ((uint32_t)((t >> 5) * 32) << 16) + kATmemBase + (uint32_t)gi * kATmemCols, v);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) { mbar_arrive(b_afull + 8 * gi); mbar_arrive(b_rawempty + 8 * sr); }
-            } else {
-#pragma unroll
-            for (int j = 0; j < kItemsPerThread; j++) {
-                const int item = t + j * kGroupThreads;
-                const uint32_t o2 = j * (kGroupThreads / 4) * 128;
-                const GemmTensor& T = P.t[tr.ti];
-                if (P.neg_base) decode_item<1>(rawp, Ap, item, off_lo + o2, off_hi + o2, T.base2, T, tr.mt * kTileRows, kb * kTK);
-                else decode_item<0>(rawp, Ap, item, off_lo + o2, off_hi + o2, T.base2, T, tr.mt * kTileRows, kb * kTK);
-            }
-            fence_async_smem();                                   // generic-proxy writes -> visible to the MMA
+            if (t == 0) GT(it - rg.lo, 13 + 5 * gi);
+            if (dt == 0 && it == rg.lo) GP(2);
+            RawRow q;
+            load_raw_row(raw + sr * kRawBytes, t, gi, q);
             __syncwarp();
-            if (lane == 0) { mbar_arrive(b_afull + 8 * gi); mbar_arrive(b_rawempty + 8 * sr); }
+            if (t == 0) GT(it - rg.lo, 14 + 5 * gi);
+            if (lane == 0) mbar_arrive(b_rawempty + 8 * sr);      // the stage is free once it sits in registers
+            const GemmTensor& T = P.t[tr.ti];
+            uint32_t v[32];
+#ifdef S12_GEMM_NODECODE
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = i < 16 ? (&q.s[0].x)[i] : (&q.g[0].x)[i & 7];
+#else
+            if (P.neg_base) decode_row<1>(q, T.base2, v);
+            else decode_row<0>(q, T.base2, v);
+            esc_apply(esc, T, kb * kBigK + gi * kTK, v);
+#endif
+            if (t == 0) GT(it - rg.lo, 15 + 5 * gi);
+            if (wo > 0) mbar_wait(b_free + 8 * gi, (wo - 1) & 1, P.status, 0x400u, &s_abort);
+            if (t == 0) GT(it - rg.lo, 16 + 5 * gi);
+            tc_fence_after();
+            tmem_st32(a_dst, v);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_full + 8 * gi);
+            if (t == 0) GT(it - rg.lo, 17 + 5 * gi);
+            if (dt == 0 && it == rg.hi - 1) GP(3);
+            if (kb + 1 == KB || it + 1 == rg.hi) {                // last raw stage of a tile segment
+                if (!two_acc) {
+                    mbar_wait(b_accfull, (uint32_t)nacc & 1, P.status, 0x1000u, &s_abort);
+                    tc_fence_after();
+                    grid_dependency_wait();                       // the output buffer may still be in use
+                    const int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
+                    float* wsp = P.ws + ((size_t)blockIdx.x * 2 + (nacc == 0 ? 0 : 1)) * (size_t)BN * kTileRows;
+                    drain_chunks(P, T, tmem_base + ((uint32_t)((t >> 5) * 32) << 16), gi + 1, kDrainTeams,
+                                 seg_kb0 == 0 && kb + 1 == KB, tr.mt * kTileRows + t, t, nt * BN, wsp);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(b_accempty);
+                }
+                nacc++;
+                seg_kb0 = 0;
             }
-            sr += kDecodeGroups;
-            while (sr >= kRawStages) { sr -= kRawStages; wr++; }
+            if (++sr == kRawStages) { sr = 0; wr++; }
             wo++;
-            kb += kDecodeGroups;
-            if (kb >= KB) {
-                while (kb >= KB) { kb -= KB; tile++; }
+            if (++kb == KB) {
+                kb = 0; tile++;
                 tr = locate_mtile(P, tile / P.n_ntiles);
+                if (it + 1 < rg.hi) esc_seek(esc, P.t[tr.ti], tr.mt * kTileRows + t, gi * kTK);
             }
         }
     } else if (warp >= kFirstEpiWarp) {
@@ -478,35 +539,18 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             const int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
             const TileRef tr = locate_mtile(P, mtg);
             const GemmTensor& T = P.t[tr.ti];
-            const int mt = tr.mt;
             const int buf = two_acc ? (nacc & 1) : 0;
             const int uses = two_acc ? (nacc >> 1) : nacc;
             mbar_wait(b_accfull + 8 * buf, uses & 1, P.status, 0x800u, &s_abort);
             tc_fence_after();
             const int b0 = nt * BN;
+            const int m = tr.mt * kTileRows + mrow;
             // A segment that covers only part of its tile's K range goes to the
             // workspace (slot 0: the tile this CTA's range starts in, slot 1: the
             // tile it ends in) and is summed by gemm_reduce_kernel.
             float* wsp = P.ws + ((size_t)blockIdx.x * 2 + (it == rg.lo ? 0 : 1)) * (size_t)BN * kTileRows;
-            for (int hc = 0; hc < kHalves * ((BN + 31) / 32); hc++) {
-                const int nch = (BN + 31) / 32, h = hc / nch, c0 = (hc - h * nch) * 32;
-                const int m = mt * kTileRows + h * kTM + mrow;
-                const int tr = h * kTM + mrow;                    // row inside the CTA tile
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kHalves * BN + h * BN + c0), v);
-                tmem_ld_wait();
-                if (whole) {
-                    if (m < T.M) {
-#pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (b0 + c0 + j < P.B) T.out[(size_t)(b0 + c0 + j) * T.out_stride + m] = __uint_as_float(v[j]);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (c0 + j < BN) wsp[(size_t)(c0 + j) * kTileRows + tr] = __uint_as_float(v[j]);
-                }
-            }
+            drain_chunks(P, T, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), 0, two_acc ? 1 : kDrainTeams,
+                         whole, m, mrow, b0, wsp);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(b_accempty + 8 * buf);     // accumulator may be overwritten
@@ -514,11 +558,13 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             it = seg_end;
             tile++;
         }
+        if (warp == kFirstEpiWarp && lane == 0) GP(4);
     }
 
     tc_fence_before();
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
+    if (threadIdx.x == 0) GP(5);
 }
 
 // Sums the partial accumulators of every tile whose K range was shared by
@@ -530,15 +576,29 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
 {
     grid_launch_dependents();
     grid_dependency_wait();
-    const int tile = blockIdx.x, KB = P.KB, BN = P.BN;
+#ifdef S12_GEMM_TRACE
+    if (threadIdx.x == 0) atomicMin(&g_gphase[160][0], gt_now());
+    struct AtExit { __device__ ~AtExit() { if (threadIdx.x == 0) atomicMax(&g_gphase[160][1], gt_now()); } } at_exit;
+#endif
+    // CTA c looks at the end of GEMM CTA c's range: if it cuts a tile and c is the first CTA
+    // working on that tile, this CTA sums the tile's partials
+    const int KB = P.KB, BN = P.BN;
     const long long T = (long long)P.n_mtiles * P.n_ntiles * KB;
-    const int tile_lo = tile * KB, tile_end = tile_lo + KB;
-    int c_first = (int)(((long long)tile_lo * G) / T);
-    while (c_first > 0 && cta_range(T, G, c_first).lo > tile_lo) c_first--;
-    while (cta_range(T, G, c_first).hi <= tile_lo) c_first++;
-    int c_last = c_first;
+    const int c_first = blockIdx.x;
+    const Range r0 = cta_range(T, G, c_first);
+    if (r0.hi % KB == 0) return;
+    const int tile = r0.hi / KB, tile_lo = tile * KB, tile_end = tile_lo + KB;
+    if (r0.lo > tile_lo) return;
+    int c_last = c_first + 1;
     while (c_last + 1 < G && cta_range(T, G, c_last + 1).lo < tile_end) c_last++;
-    if (c_first == c_last) return;
+    const int nparts = c_last - c_first + 1;
+    __shared__ const float* s_part[192];
+    for (int i = threadIdx.x; i < nparts; i += blockDim.x) {
+        const int c = c_first + i;
+        const int slot = cta_range(T, G, c).lo >= tile_lo ? 0 : 1;
+        s_part[i] = P.ws + ((size_t)c * 2 + slot) * (size_t)BN * kTileRows;
+    }
+    __syncthreads();
     const int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
     const TileRef tr = locate_mtile(P, mtg);
     const GemmTensor& W = P.t[tr.ti];
@@ -549,10 +609,8 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
     for (int j = blockIdx.y * 32 + threadIdx.x / kRowLanes; j < blockIdx.y * 32 + 32 && j < BN; j += 256 / kRowLanes) {
         if (b0 + j >= P.B) break;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = c_first; c <= c_last; c++) {
-            const int slot = cta_range(T, G, c).lo >= tile_lo ? 0 : 1;
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(
-                P.ws + ((size_t)c * 2 + slot) * (size_t)BN * kTileRows + (size_t)j * kTileRows + m4));
+        for (int i = 0; i < nparts; i++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(s_part[i] + (size_t)j * kTileRows + m4));
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         const int m = mt * kTileRows + m4;
@@ -573,7 +631,7 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
 // ----------------------------------------------------------------------------
 static size_t gemm_smem_bytes(int BN)
 {
-    return (size_t)kRawStages * kRawBytes + (size_t)kASmemBytes + (size_t)kXStages * BN * 128 +
+    return (size_t)kRawStages * kRawBytes + (size_t)kXStages * BN * 128 +
            8 * kNumBars + 16 + 1024;
 }
 
@@ -636,7 +694,7 @@ static int get_scratch(size_t ws_bytes, Scratch& out, const char* who)
 int gemm_tc_supported(const S12Tensor* w, int act_stride, int out_stride, int B)
 {
     (void)out_stride;
-    if (B <= 16 || w->M < 1 || w->K < kTK) return 0;
+    if (B <= 16 || w->M < 1 || w->K < kBigK) return 0;
     if (w->K % 32 != 0 || act_stride % 8 != 0) return 0;
     if (w->base_exp < -1 || w->base_exp > 240) return 0;
     if (reinterpret_cast<uintptr_t>(w->sm) % 16 || reinterpret_cast<uintptr_t>(w->gr) % 16) return 0;
@@ -652,7 +710,7 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
     P.BN = B >= 256 ? 256 : ((B + 15) / 16) * 16;
     if (P.BN < 32) P.BN = 32;
     P.n_ntiles = (B + P.BN - 1) / P.BN;
-    P.KB = (P.K + kTK - 1) / kTK;
+    P.KB = (P.K + kBigK - 1) / kBigK;
     P.neg_base = 0;
     int mtiles = 0;
     for (int i = 0; i < nt; i++) {
@@ -666,9 +724,9 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
         mtiles += (s.M + kTileRows - 1) / kTileRows;
         t.mtile_end = mtiles;
         if (!make_map(&maps.sm[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, s.sm, (uint64_t)s.K, (uint64_t)s.M, (uint64_t)s.K,
-                      kTK, kTileRows, kATmem ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                      128, kTileRows, CU_TENSOR_MAP_SWIZZLE_128B) ||
             !make_map(&maps.gr[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, s.gr, (uint64_t)s.K / 2, (uint64_t)s.M, (uint64_t)s.K / 2,
-                      kTK / 2, kTileRows, kATmem ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE))
+                      128, kTileRows, CU_TENSOR_MAP_SWIZZLE_128B))
             return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
     }
     for (int i = nt; i < kMaxGemmTensors; i++) { maps.sm[i] = maps.sm[0]; maps.gr[i] = maps.gr[0]; }
@@ -676,9 +734,7 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
     if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)P.K, (uint64_t)B, (uint64_t)act_stride * 2,
                   kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
-    uint32_t cols = 32;
-    while (cols < (uint32_t)(2 * kHalves * P.BN) && cols < 512) cols <<= 1;
-    P.tmem_cols = kATmem ? 512u : cols;
+    P.tmem_cols = 512u;                  // accumulators below kATmemBase, the A stages above
     return S12_OK;
 }
 
@@ -697,8 +753,8 @@ int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_st
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: problem too large for the tile schedule", who);
     const int sms = sm_count();
     int grid = T < sms ? (int)T : sms;
-    // do not cut tiles finer than ~8 K blocks per CTA: the fix-up traffic would dominate
-    const long long min_iters = 8;
+    // do not cut tiles finer than 2 raw stages (512 columns) per CTA: the fix-up traffic would dominate
+    const long long min_iters = 2;
     if (T / grid < min_iters) grid = (int)((T + min_iters - 1) / min_iters);
     if (grid < 1) grid = 1;
     Scratch sc;
@@ -725,7 +781,7 @@ int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_st
     }
     rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, maps, mx, P);
     if (rc || !partial) return rc;
-    return launch(gemm_reduce_kernel, dim3(P.n_mtiles * P.n_ntiles, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
+    return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
 }
 
 int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
@@ -804,8 +860,8 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     if (B > kNoAllocMaxB)
         return fail(S12_ERR_TOO_LARGE, "%s: B=%d exceeds the maximum of %d sequences per call", who, B, kNoAllocMaxB);
     if (B <= 16) return fail(S12_ERR_UNSUPPORTED, "%s: B=%d; this entry point covers 17..%d (smaller batches need no scratch: use s12_gemv_batched_async)", who, B, kNoAllocMaxB);
-    if (w->M < 1 || w->K < kTK || (w->K % 32) != 0 || (act_stride % 8) != 0 || act_stride < w->K || out_stride < w->M)
-        return fail(S12_ERR_UNSUPPORTED, "%s: needs M>=1, K>=64, K%%32==0, act_stride%%8==0, act_stride>=K, out_stride>=M", who);
+    if (w->M < 1 || w->K < kBigK || (w->K % 32) != 0 || (act_stride % 8) != 0 || act_stride < w->K || out_stride < w->M)
+        return fail(S12_ERR_UNSUPPORTED, "%s: needs M>=1, K>=256, K%%32==0, act_stride%%8==0, act_stride>=K, out_stride>=M", who);
     if (w->base_exp < -1 || w->base_exp > 240) return fail(S12_ERR_BAD_ARG, "%s: base_exp=%d", who, w->base_exp);
     if (!w->sm || !w->gr || reinterpret_cast<uintptr_t>(w->sm) % 16 || reinterpret_cast<uintptr_t>(w->gr) % 16 ||
         reinterpret_cast<uintptr_t>(act) % 16)
@@ -831,7 +887,7 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     // CTAs: as the regular path, then capped so that two partial tiles per CTA fit the fixed scratch
     const int sms = sm_count();
     int grid = T < sms ? (int)T : sms;
-    if (T / grid < 8) grid = (int)((T + 7) / 8);
+    if (T / grid < 2) grid = (int)((T + 1) / 2);
     const size_t per_cta = (size_t)2 * P.BN * kTileRows;
     const int fit = (int)(kNoAllocWsFloats / per_cta);
     if (grid > fit) grid = fit;
@@ -842,5 +898,5 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     const size_t smem = gemm_smem_bytes(P.BN);
     rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, maps, mx, P);
     if (rc || !partial) return rc;
-    return launch(gemm_reduce_kernel, dim3(P.n_mtiles, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
+    return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
 }
