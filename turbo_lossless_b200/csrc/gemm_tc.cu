@@ -39,6 +39,7 @@
 // (nvidia_kernels.cu:533-584).
 #include "common.cuh"
 #include <cuda.h>
+#include <algorithm>
 #include <mutex>
 
 namespace s12 {
@@ -101,7 +102,8 @@ struct GemmParams {
     unsigned int* status;
     int K, B;
     int BN;                     // sequences per tile (multiple of 16, <= 256)
-    int n_mtiles, n_ntiles, KB; // row tiles of all tensors, sequence tiles, K blocks per tile
+    int n_mtiles, n_ntiles, KB; // row tiles of all tensors, sequence tiles, raw stages (256 columns) per tile
+    int split;                  // 0: stream-K ranges, >= 1: tiles cut into this many fixed parts
     int neg_base;               // some base_exp < 0: decode mode 1
     uint32_t tmem_cols;
 };
@@ -123,6 +125,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
 {
@@ -196,14 +202,33 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------
-// schedule shared by all roles: this CTA's contiguous range [lo, hi) of
-// (tile, K block) iterations, walked tile by tile; tile t covers iterations
-// [t*KB, (t+1)*KB)
+// schedule shared by all roles: CTA c of G works on the contiguous range
+// [lo, hi) of (tile, raw stage) iterations, walked tile by tile; tile t covers
+// iterations [t*KB, (t+1)*KB).  Two ways of cutting the iteration space:
+//   split == 0  stream-K: equal ranges, cut anywhere (up to two partial tiles
+//               per CTA)
+//   split >= 1  every tile is cut into `split` parts at fixed places and the
+//               CTAs take whole parts; split == 1 means whole tiles, no
+//               partials at all
 // ----------------------------------------------------------------------------
 struct Range { int lo, hi; };
-__host__ __device__ __forceinline__ Range cta_range(long long T, int G, int cta)
+__host__ __device__ __forceinline__ int part_start(long long p, int split, int KB)
 {
-    return Range{(int)(T * cta / G), (int)(T * (cta + 1) / G)};
+    const long long t = p / split;
+    const int j = (int)(p - t * split);
+    return (int)(t * KB) + (int)(((long long)j * KB) / split);
+}
+__host__ __device__ __forceinline__ Range cta_range(const GemmParams& P, int G, int cta)
+{
+    const long long tiles = (long long)P.n_mtiles * P.n_ntiles;
+    if (P.split == 0) {
+        const long long T = tiles * P.KB;
+        if (T < (1 << 20) && G <= 2048)                           // the usual case fits 32-bit division
+            return Range{(int)((unsigned)T * (unsigned)cta / (unsigned)G), (int)((unsigned)T * (unsigned)(cta + 1) / (unsigned)G)};
+        return Range{(int)(T * cta / G), (int)(T * (cta + 1) / G)};
+    }
+    const long long parts = tiles * P.split;
+    return Range{part_start(parts * cta / G, P.split, P.KB), part_start(parts * (cta + 1) / G, P.split, P.KB)};
 }
 
 // Walks one row's CSR escape list in column order, two entries ahead of the
@@ -253,35 +278,26 @@ __device__ __forceinline__ void esc_apply(EscCursor& e, const GemmTensor& T, int
     }
 }
 
-// One thread's share of a raw stage: row r, 64 columns of K block `sub` = 64 sm
-// bytes and 32 gr bytes.  The raw boxes carry the 128-byte swizzle: 16-byte
-// chunk j of row r sits at chunk j ^ (r & 7).
-struct RawRow { uint4 s[4]; uint4 g[2]; };
-__device__ __forceinline__ void load_raw_row(const uint8_t* raw, int r, int sub, RawRow& q)
+// One thread decodes its share of a raw stage (row r, the 64 columns of K block
+// `sub` = 64 sm bytes and 32 gr bytes) into 32 registers of bf16 pairs in k
+// order (= 32 TMEM columns of the thread's lane); escapes get the exponent
+// base_exp.  The raw boxes carry the 128-byte swizzle: 16-byte chunk j of row r
+// sits at chunk j ^ (r & 7).  Reading chunk by chunk keeps few raw registers live.
+template <int kMode>
+__device__ __forceinline__ void decode_row(const uint8_t* raw, int r, int sub, uint32_t base2, uint32_t (&v)[32])
 {
     const uint8_t* srow = raw + (sub >> 1) * kRawBoxBytes + r * 128;
     const uint8_t* grow = raw + 2 * kRawBoxBytes + r * 128;
     const int sw = r & 7, sc = (sub & 1) * 4, gc = sub * 2;
 #pragma unroll
-    for (int c = 0; c < 4; c++) q.s[c] = *reinterpret_cast<const uint4*>(srow + (((sc + c) ^ sw) << 4));
-#pragma unroll
-    for (int c = 0; c < 2; c++) q.g[c] = *reinterpret_cast<const uint4*>(grow + (((gc + c) ^ sw) << 4));
-}
-
-// Decodes the 64 weights of a RawRow into 32 registers of bf16 pairs in k order
-// (= 32 TMEM columns of the thread's lane); escapes get the exponent base_exp.
-template <int kMode>
-__device__ __forceinline__ void decode_row(const RawRow& q, uint32_t base2, uint32_t (&v)[32])
-{
-#pragma unroll
     for (int c = 0; c < 4; c++) {                                // 16 columns per chunk
-        const uint4 s = q.s[c];
-        const uint32_t gx = (c & 1) ? q.g[c >> 1].z : q.g[c >> 1].x, gy = (c & 1) ? q.g[c >> 1].w : q.g[c >> 1].y;
+        const uint4 s = *reinterpret_cast<const uint4*>(srow + (((sc + c) ^ sw) << 4));
+        const uint2 g = *reinterpret_cast<const uint2*>(grow + (((gc + (c >> 1)) ^ sw) << 4) + (c & 1) * 8);
         uint32_t p[4];
-        decode8<kMode>(s.x, s.y, gx, base2, p);
+        decode8<kMode>(s.x, s.y, g.x, base2, p);
         v[8 * c + 0] = prmt(p[0], p[1], 0x5410u); v[8 * c + 1] = prmt(p[2], p[3], 0x5410u);
         v[8 * c + 2] = prmt(p[0], p[1], 0x7632u); v[8 * c + 3] = prmt(p[2], p[3], 0x7632u);
-        decode8<kMode>(s.z, s.w, gy, base2, p);
+        decode8<kMode>(s.z, s.w, g.y, base2, p);
         v[8 * c + 4] = prmt(p[0], p[1], 0x5410u); v[8 * c + 5] = prmt(p[2], p[3], 0x5410u);
         v[8 * c + 6] = prmt(p[0], p[1], 0x7632u); v[8 * c + 7] = prmt(p[2], p[3], 0x7632u);
     }
@@ -351,6 +367,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     __shared__ int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool two_acc = 2 * BN <= (int)kATmemBase;              // accumulators double buffered
+
     if (threadIdx.x == 0) {
         GP(0);
         s_abort = 0;
@@ -359,6 +376,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
         for (int i = 0; i < 2; i++) { mbar_init(b_accfull + 8 * i, 1); mbar_init(b_accempty + 8 * i, two_acc ? 4 : 4 + kDecodeWarps); }
         mbar_fence_init();
     }
+    if (threadIdx.x == 64) { prefetch_tensormap(&map_x); }
     if (warp == 1) { tmem_alloc(smem_addr(tmem_slot), P.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
@@ -370,7 +388,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     // The schedule counts raw stages ("big blocks" of kBigK columns); a tile has
     // KB of them, the last one zero-filled by TMA past column K.
     const int KB = P.KB;
-    const Range rg = cta_range((long long)P.n_mtiles * P.n_ntiles * KB, gridDim.x, blockIdx.x);
+    const Range rg = cta_range(P, gridDim.x, blockIdx.x);
     const int tile0 = rg.lo / KB, kb0 = rg.lo - tile0 * KB;     // the only divisions of the schedule
 
     if (warp == 0) {
@@ -476,21 +494,14 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             mbar_wait(b_rawfull + 8 * sr, wr & 1, P.status, 0x200u, &s_abort);
             if (t == 0) GT(it - rg.lo, 13 + 5 * gi);
             if (dt == 0 && it == rg.lo) GP(2);
-            RawRow q;
-            load_raw_row(raw + sr * kRawBytes, t, gi, q);
-            __syncwarp();
-            if (t == 0) GT(it - rg.lo, 14 + 5 * gi);
-            if (lane == 0) mbar_arrive(b_rawempty + 8 * sr);      // the stage is free once it sits in registers
             const GemmTensor& T = P.t[tr.ti];
             uint32_t v[32];
-#ifdef S12_GEMM_NODECODE
-#pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = i < 16 ? (&q.s[0].x)[i] : (&q.g[0].x)[i & 7];
-#else
-            if (P.neg_base) decode_row<1>(q, T.base2, v);
-            else decode_row<0>(q, T.base2, v);
+            if (P.neg_base) decode_row<1>(raw + sr * kRawBytes, t, gi, T.base2, v);
+            else decode_row<0>(raw + sr * kRawBytes, t, gi, T.base2, v);
+            __syncwarp();
+            if (t == 0) GT(it - rg.lo, 14 + 5 * gi);
+            if (lane == 0) mbar_arrive(b_rawempty + 8 * sr);      // this warp has read its share of the stage
             esc_apply(esc, T, kb * kBigK + gi * kTK, v);
-#endif
             if (t == 0) GT(it - rg.lo, 15 + 5 * gi);
             if (wo > 0) mbar_wait(b_free + 8 * gi, (wo - 1) & 1, P.status, 0x400u, &s_abort);
             if (t == 0) GT(it - rg.lo, 16 + 5 * gi);
@@ -569,8 +580,9 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
 
 // Sums the partial accumulators of every tile whose K range was shared by
 // several CTAs, in CTA order (deterministic), and stores the result.  One CTA
-// per (tile, 32-sequence slab); tiles owned by a single CTA were stored by the
-// GEMM kernel itself and exit at once.
+// per (range boundary, 32-sequence slab); boundaries that cut no tile exit at
+// once.
+constexpr int kReduceCols = 32;                                  // sequences per CTA of the fix-up pass
 __global__ void __launch_bounds__(256)
 gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
 {
@@ -583,19 +595,18 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
     // CTA c looks at the end of GEMM CTA c's range: if it cuts a tile and c is the first CTA
     // working on that tile, this CTA sums the tile's partials
     const int KB = P.KB, BN = P.BN;
-    const long long T = (long long)P.n_mtiles * P.n_ntiles * KB;
     const int c_first = blockIdx.x;
-    const Range r0 = cta_range(T, G, c_first);
+    const Range r0 = cta_range(P, G, c_first);
     if (r0.hi % KB == 0) return;
     const int tile = r0.hi / KB, tile_lo = tile * KB, tile_end = tile_lo + KB;
     if (r0.lo > tile_lo) return;
     int c_last = c_first + 1;
-    while (c_last + 1 < G && cta_range(T, G, c_last + 1).lo < tile_end) c_last++;
+    while (c_last + 1 < G && cta_range(P, G, c_last + 1).lo < tile_end) c_last++;
     const int nparts = c_last - c_first + 1;
     __shared__ const float* s_part[192];
     for (int i = threadIdx.x; i < nparts; i += blockDim.x) {
         const int c = c_first + i;
-        const int slot = cta_range(T, G, c).lo >= tile_lo ? 0 : 1;
+        const int slot = cta_range(P, G, c).lo >= tile_lo ? 0 : 1;
         s_part[i] = P.ws + ((size_t)c * 2 + slot) * (size_t)BN * kTileRows;
     }
     __syncthreads();
@@ -606,11 +617,21 @@ gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
     constexpr int kRowLanes = kTileRows / 4;                     // threads across the rows of a tile
     const int m4 = (threadIdx.x % kRowLanes) * 4;                // four consecutive rows per thread
     const int b0 = nt * BN;
-    for (int j = blockIdx.y * 32 + threadIdx.x / kRowLanes; j < blockIdx.y * 32 + 32 && j < BN; j += 256 / kRowLanes) {
+    for (int j = blockIdx.y * kReduceCols + threadIdx.x / kRowLanes; j < (blockIdx.y + 1) * kReduceCols && j < BN;
+         j += 256 / kRowLanes) {
         if (b0 + j >= P.B) break;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int i = 0; i < nparts; i++) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(s_part[i] + (size_t)j * kTileRows + m4));
+        const size_t off = (size_t)j * kTileRows + m4;
+        int i = 0;
+        for (; i + 4 <= nparts; i += 4) {                        // four loads in flight, summed in CTA order
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = __ldcg(reinterpret_cast<const float4*>(s_part[i + u] + off));
+#pragma unroll
+            for (int u = 0; u < 4; u++) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+        }
+        for (; i < nparts; i++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(s_part[i] + off));
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         const int m = mt * kTileRows + m4;
@@ -738,6 +759,44 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
     return S12_OK;
 }
 
+static int gemm_env_int(const char* name, int dflt)
+{
+    const char* e = getenv(name);
+    return (e && *e) ? atoi(e) : dflt;
+}
+
+// Picks how the iteration space is cut (P.split) and the number of CTAs, at most
+// max_grid, by a small cost model in microseconds whose constants were measured
+// on this kernel: a raw stage takes ~1.25 us, every tile segment of a CTA costs
+// ~3 us of pipeline drain and refill, and the fix-up pass costs its launch plus
+// reading the partial tiles (which mostly still sit in L2).
+static int choose_schedule(GemmParams& P, int max_grid)
+{
+    const long long tiles = (long long)P.n_mtiles * P.n_ntiles, T = tiles * P.KB;
+    const double tb = 1.25, seg = 3.0, tile_mb = (double)P.BN * kTileRows * 4 / 1e6;
+    auto fixup = [&](double nparts) { return 2.5 + nparts * tile_mb / 5.5; };
+    // stream-K, never finer than 2 raw stages per CTA
+    int best_grid = (int)std::min<long long>(max_grid, std::max<long long>(1, T / 2));
+    int best_split = 0;
+    double per = (double)T / best_grid;
+    double best = per * tb + seg * (1.0 + per / P.KB) + (best_grid > 1 ? fixup(2.0 * best_grid) : 0.0);
+    const int forced = gemm_env_int("S12_GEMM_SPLIT", -1);           // tuning knob: -1 model, 0 stream-K, n parts per tile
+    // Fixed parts: measured, only whole tiles in a single round beat stream-K (CTAs that switch tiles
+    // all at once collide in their drains; staggered stream-K ranges do not).  Other values of the
+    // knob remain for experiments.
+    for (int s = 1; s <= 8 && s * 2 <= std::max(2, P.KB); s++) {
+        const long long parts = tiles * s;
+        const int G = (int)std::min<long long>(max_grid, parts);
+        const double rounds = (double)((parts + G - 1) / G);
+        const double t = rounds * (((P.KB + s - 1) / s) * tb + seg) + (s > 1 ? fixup((double)parts) : 0.0);
+        const bool allowed = s == 1 && parts <= max_grid;
+        if ((forced < 0 && allowed && t < best) || forced == s) { best = t; best_grid = G; best_split = s; }
+    }
+    if (forced == 0) { best_split = 0; best_grid = (int)std::min<long long>(max_grid, std::max<long long>(1, T / 2)); }
+    P.split = best_split;
+    return best_grid;
+}
+
 int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_stride, void* const* outs,
                          const int* out_strides, int B, void* stream, const char* who)
 {
@@ -752,18 +811,14 @@ int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_st
     const long long T = (long long)P.n_mtiles * P.n_ntiles * P.KB;
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: problem too large for the tile schedule", who);
     const int sms = sm_count();
-    int grid = T < sms ? (int)T : sms;
-    // do not cut tiles finer than 2 raw stages (512 columns) per CTA: the fix-up traffic would dominate
-    const long long min_iters = 2;
-    if (T / grid < min_iters) grid = (int)((T + min_iters - 1) / min_iters);
-    if (grid < 1) grid = 1;
+    const int grid = choose_schedule(P, sms);
     Scratch sc;
     rc = get_scratch((size_t)sms * 2 * 256 * kTileRows * sizeof(float), sc, who);   // sized for the largest launch
     if (rc) return rc;
     P.ws = sc.ws;
     // does any tile have its K range shared between CTAs?
     bool partial = false;
-    for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(T, grid, c).hi % P.KB != 0;
+    for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(P, grid, c).hi % P.KB != 0;
 
     const size_t smem = gemm_smem_bytes(P.BN);
     static bool attr_set[64];
@@ -781,7 +836,7 @@ int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_st
     }
     rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, maps, mx, P);
     if (rc || !partial) return rc;
-    return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
+    return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + kReduceCols - 1) / kReduceCols), dim3(256), 0, stream, who, P, grid);
 }
 
 int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
@@ -885,18 +940,14 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: M*K exceeds the tile schedule's range", who);
 
     // CTAs: as the regular path, then capped so that two partial tiles per CTA fit the fixed scratch
-    const int sms = sm_count();
-    int grid = T < sms ? (int)T : sms;
-    if (T / grid < 2) grid = (int)((T + 1) / 2);
     const size_t per_cta = (size_t)2 * P.BN * kTileRows;
     const int fit = (int)(kNoAllocWsFloats / per_cta);
-    if (grid > fit) grid = fit;
-    if (grid < 1) grid = 1;
+    const int grid = choose_schedule(P, std::max(1, std::min(sm_count(), fit)));
     bool partial = false;
-    for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(T, grid, c).hi % P.KB != 0;
+    for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(P, grid, c).hi % P.KB != 0;
 
     const size_t smem = gemm_smem_bytes(P.BN);
     rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, maps, mx, P);
     if (rc || !partial) return rc;
-    return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + 31) / 32), dim3(256), 0, stream, who, P, grid);
+    return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + kReduceCols - 1) / kReduceCols), dim3(256), 0, stream, who, P, grid);
 }
