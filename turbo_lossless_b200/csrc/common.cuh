@@ -20,19 +20,34 @@ unsigned int* device_status_word();                 // per-device status word (d
 // carries the programmatic-stream-serialization attribute so that the kernel
 // may begin before its predecessor in the stream has finished.
 template <typename... KArgs, typename... Args>
-int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
-           const char* name, Args... args)
+int launch_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
+                     const char* name, int cluster_x, Args... args)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem;
     cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    int n = 0;
     if (dependent_launch_enabled()) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
     }
+    if (cluster_x > 1) {                 // thread-block clusters of cluster_x consecutive CTAs
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    cfg.attrs = attr; cfg.numAttrs = (unsigned)n;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...), name);
+}
+template <typename... KArgs, typename... Args>
+int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
+           const char* name, Args... args)
+{
+    return launch_clustered(kernel, grid, block, smem, stream, name, 1, args...);
 }
 
 // ---------------------------------------------------------------------------

@@ -75,7 +75,7 @@ static_assert(kGroupThreads == kTM, "one decode thread per tile row");
 __device__ long long g_gtrace[64][48];
 #define GT(i, slot) do { if (blockIdx.x == 0 && (i) < 64) g_gtrace[(i)][(slot)] = clock64(); } while (0)
 // wall-clock (ns) stamps of kernel phases, per CTA; row 160 = reduce kernel (min start, max end)
-__device__ unsigned long long g_gphase[161][8];
+__device__ unsigned long long g_gphase[161][12];
 __device__ __forceinline__ unsigned long long gt_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 #define GP(slot) do { g_gphase[blockIdx.x][(slot)] = gt_now(); } while (0)
 #else
@@ -104,6 +104,8 @@ struct GemmParams {
     int BN;                     // sequences per tile (multiple of 16, <= 256)
     int n_mtiles, n_ntiles, KB; // row tiles of all tensors, sequence tiles, raw stages (256 columns) per tile
     int split;                  // 0: stream-K ranges, >= 1: tiles cut into this many fixed parts
+    int cluster;                // > 1: the `split` parts of a tile run as one thread-block cluster and add
+                                // their accumulators through distributed shared memory (no workspace)
     int neg_base;               // some base_exp < 0: decode mode 1
     uint32_t tmem_cols;
 };
@@ -129,6 +131,30 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// all threads of all CTAs of the cluster; orders shared-memory accesses across the cluster
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of this CTA's shared-memory location `addr` in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr)
+{
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
 {
@@ -336,11 +362,80 @@ __device__ __forceinline__ void drain_chunks(const GemmParams& P, const GemmTens
     }
 }
 
+constexpr int kDrainTeams = 1 + kDecodeGroups;   // per lane quarter: the epilogue warp and one warp of each decode group
+
+// Cluster reduction, run by all threads of a CTA after its roles have finished.
+// The cs CTAs of the cluster hold partial accumulators of one tile (their ranges
+// are the tile's cs parts).  Every CTA moves its accumulator from tensor memory
+// into its own shared memory (the operand rings are dead by then); 32-column
+// chunk c of the tile then belongs to rank c % cs, which reads that chunk from
+// all cs CTAs through distributed shared memory, adds the partials in rank order
+// and stores the result.  Kept out of line so that its registers do not weigh on
+// the decode loop.
+__device__ __noinline__ void cluster_reduce(const GemmParams& P, uint8_t* smem, uint32_t tmem_base, uint32_t b_accfull,
+                                            int* s_abort)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int BN = P.BN, cs = P.cluster;
+    const int tile0 = cta_range(P, gridDim.x, blockIdx.x).lo / P.KB;
+    const int nch = (BN + 31) / 32;
+    float* xbuf = reinterpret_cast<float*>(smem);                 // [chunk][32 columns][128 rows]
+    __syncwarp();
+    if (warp >= kFirstDecodeWarp) {
+        mbar_wait(b_accfull, 0, P.status, 0x2000u, s_abort);      // all MMAs of this CTA have finished
+        tc_fence_after();
+        if (warp == kFirstEpiWarp && lane == 0) GP(6);
+        const int q = warp & 3, mrow = q * 32 + lane;
+        const int team = warp >= kFirstEpiWarp ? 0 : 1 + (warp - kFirstDecodeWarp) / 4;
+        for (int c = team; c < nch; c += kDrainTeams) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+            tmem_ld_wait();
+            float* dst = xbuf + (size_t)c * 32 * kTileRows + mrow;
+#pragma unroll
+            for (int j = 0; j < 32; j++) dst[j * kTileRows] = __uint_as_float(v[j]);
+        }
+    }
+    if (warp == kFirstEpiWarp && lane == 0) GP(7);
+    cluster_sync_all();                                           // every CTA of the cluster has staged its partial tile
+    if (warp == kFirstEpiWarp && lane == 0) GP(8);
+    const uint32_t rank = cluster_ctarank();
+    grid_dependency_wait();                                       // the output buffer may still be in use
+    const int mtg = tile0 / P.n_ntiles, nt = tile0 - mtg * P.n_ntiles;
+    const TileRef tr = locate_mtile(P, mtg);
+    const GemmTensor& T = P.t[tr.ti];
+    const int nlc = (nch + cs - 1) / cs;                          // chunks owned by a rank, at most
+    for (int idx = threadIdx.x; idx < nlc * 32 * (kTileRows / 4); idx += kGemmThreads) {
+        const int r4 = (idx % (kTileRows / 4)) * 4, j = (idx / (kTileRows / 4)) & 31, lc = idx / (32 * (kTileRows / 4));
+        const int c = lc * cs + (int)rank;
+        const int b = nt * BN + c * 32 + j;
+        if (c >= nch || c * 32 + j >= BN || b >= P.B) continue;
+        const uint32_t local = smem_addr(xbuf + ((size_t)c * 32 + j) * kTileRows + r4);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < cs; s++) {
+            const float4 v = ld_cluster_f4(map_to_cta(local, (uint32_t)s));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int m = tr.mt * kTileRows + r4;
+        float* dst = T.out + (size_t)b * T.out_stride + m;
+        if (m + 3 < T.M && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            *reinterpret_cast<float4*>(dst) = acc;
+        } else {
+            if (m < T.M) dst[0] = acc.x;
+            if (m + 1 < T.M) dst[1] = acc.y;
+            if (m + 2 < T.M) dst[2] = acc.z;
+            if (m + 3 < T.M) dst[3] = acc.w;
+        }
+    }
+    if (warp == kFirstEpiWarp && lane == 0) GP(9);
+    cluster_sync_all();                                           // nobody reads this CTA's shared memory any more
+    if (warp == kFirstEpiWarp && lane == 0) GP(10);
+}
+
 // When the accumulator cannot be double buffered (BN > 192) the MMAs of the next
 // tile wait for the drain, and so does everything upstream of them.  The decode
 // warps are then idle anyway and take part in the drain: per lane quarter the
 // epilogue warp and one warp of each decode group share the chunks.
-constexpr int kDrainTeams = 1 + kDecodeGroups;
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CUtensorMap map_x,
@@ -367,6 +462,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     __shared__ int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool two_acc = 2 * BN <= (int)kATmemBase;              // accumulators double buffered
+    const int cs = P.cluster;                                    // CTAs of the cluster that share this CTA's tile
 
     if (threadIdx.x == 0) {
         GP(0);
@@ -376,7 +472,13 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
         for (int i = 0; i < 2; i++) { mbar_init(b_accfull + 8 * i, 1); mbar_init(b_accempty + 8 * i, two_acc ? 4 : 4 + kDecodeWarps); }
         mbar_fence_init();
     }
-    if (threadIdx.x == 64) { prefetch_tensormap(&map_x); }
+    if (threadIdx.x == 96) {                                     // idle warp: warm the descriptors this CTA starts with
+        const int t0 = cta_range(P, gridDim.x, blockIdx.x).lo / P.KB;
+        const TileRef r = locate_mtile(P, t0 / P.n_ntiles);
+        prefetch_tensormap(&maps.sm[r.ti]);
+        prefetch_tensormap(&maps.gr[r.ti]);
+        prefetch_tensormap(&map_x);
+    }
     if (warp == 1) { tmem_alloc(smem_addr(tmem_slot), P.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
@@ -514,7 +616,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             if (t == 0) GT(it - rg.lo, 17 + 5 * gi);
             if (dt == 0 && it == rg.hi - 1) GP(3);
             if (kb + 1 == KB || it + 1 == rg.hi) {                // last raw stage of a tile segment
-                if (!two_acc) {
+                if (!two_acc && cs <= 1) {
                     mbar_wait(b_accfull, (uint32_t)nacc & 1, P.status, 0x1000u, &s_abort);
                     tc_fence_after();
                     grid_dependency_wait();                       // the output buffer may still be in use
@@ -537,7 +639,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
                 if (it + 1 < rg.hi) esc_seek(esc, P.t[tr.ti], tr.mt * kTileRows + t, gi * kTK);
             }
         }
-    } else if (warp >= kFirstEpiWarp) {
+    } else if (warp >= kFirstEpiWarp && cs <= 1) {
         // ------------------------------ epilogue ------------------------------
         grid_dependency_wait();                                   // the output buffer may still be in use
         const int q = warp & 3;                                   // TMEM lane quarter this warp may read
@@ -571,6 +673,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
         }
         if (warp == kFirstEpiWarp && lane == 0) GP(4);
     }
+
+    if (cs > 1) cluster_reduce(P, smem, tmem_base, b_accfull, &s_abort);
 
     tc_fence_before();
     __syncthreads();
@@ -759,6 +863,53 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
     return S12_OK;
 }
 
+// Raises the kernel's dynamic shared-memory limit, once per device.
+static int ensure_smem_attr(const char* who)
+{
+    static bool attr_set[64];
+    static std::mutex mu;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = (dev < 0 || dev >= 64) ? 0 : dev;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!attr_set[dev]) {
+        cudaFuncAttributes fa;
+        int rc = check_cuda(cudaFuncGetAttributes(&fa, gemm_tc_kernel), who);
+        if (rc) return rc;
+        rc = check_cuda(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             227 * 1024 - (int)fa.sharedSizeBytes), who);
+        if (rc) return rc;
+        attr_set[dev] = true;
+    }
+    return S12_OK;
+}
+
+// How many clusters of s GEMM CTAs (one CTA per SM) the device can hold at once; 0 when the query fails.
+static int cluster_fit(int s)
+{
+    static int cache[64][9];                                     // answer + 1, 0 = not asked yet
+    static std::mutex mu;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = (dev < 0 || dev >= 64) ? 0 : dev;
+    if (s < 2 || s > 8) return 0;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cache[dev][s]) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(s * 256));
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = gemm_smem_bytes(256);
+        cudaLaunchAttribute a;
+        a.id = cudaLaunchAttributeClusterDimension;
+        a.val.clusterDim.x = (unsigned)s; a.val.clusterDim.y = 1; a.val.clusterDim.z = 1;
+        cfg.attrs = &a; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel, &cfg) != cudaSuccess) { n = 0; cudaGetLastError(); }
+        cache[dev][s] = n + 1;
+    }
+    return cache[dev][s] - 1;
+}
+
 static int gemm_env_int(const char* name, int dflt)
 {
     const char* e = getenv(name);
@@ -794,6 +945,20 @@ static int choose_schedule(GemmParams& P, int max_grid)
     }
     if (forced == 0) { best_split = 0; best_grid = (int)std::min<long long>(max_grid, std::max<long long>(1, T / 2)); }
     P.split = best_split;
+    P.cluster = 0;
+    // Few tiles (at most half as many as SMs): cut every tile into s parts that run as one cluster and add
+    // up on chip.  No workspace, no second kernel, and no CTA ever switches tiles.
+    const int cforced = gemm_env_int("S12_GEMM_CLUSTER", -1);        // tuning knob: -1 auto, 0 off, n CTAs per tile
+    const int sms = sm_count();
+    if (cforced != 0 && forced < 0 && tiles * 2 <= sms) {
+        int s = (int)std::min<long long>(std::min<long long>(sms / tiles, P.KB / 2), 8);
+        if (cforced > 0) s = std::min(cforced, std::min(P.KB, 8));
+        const size_t ring = (size_t)kRawStages * kRawBytes + (size_t)kXStages * P.BN * 128;
+        const int nch = (P.BN + 31) / 32;
+        if ((size_t)nch * 32 * kTileRows * 4 > ring) s = 0;           // a CTA stages its whole partial tile in the rings
+        while (s >= 2 && cluster_fit(s) < tiles) s--;
+        if (s >= 2) { P.split = s; P.cluster = s; return (int)(tiles * s); }
+    }
     return best_grid;
 }
 
@@ -811,6 +976,8 @@ int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_st
     const long long T = (long long)P.n_mtiles * P.n_ntiles * P.KB;
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: problem too large for the tile schedule", who);
     const int sms = sm_count();
+    rc = ensure_smem_attr(who);
+    if (rc) return rc;
     const int grid = choose_schedule(P, sms);
     Scratch sc;
     rc = get_scratch((size_t)sms * 2 * 256 * kTileRows * sizeof(float), sc, who);   // sized for the largest launch
@@ -821,21 +988,8 @@ int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_st
     for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(P, grid, c).hi % P.KB != 0;
 
     const size_t smem = gemm_smem_bytes(P.BN);
-    static bool attr_set[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    dev = (dev < 0 || dev >= 64) ? 0 : dev;
-    if (!attr_set[dev]) {
-        cudaFuncAttributes fa;
-        rc = check_cuda(cudaFuncGetAttributes(&fa, gemm_tc_kernel), who);
-        if (rc) return rc;
-        rc = check_cuda(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             227 * 1024 - (int)fa.sharedSizeBytes), who);
-        if (rc) return rc;
-        attr_set[dev] = true;
-    }
-    rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, maps, mx, P);
-    if (rc || !partial) return rc;
+    rc = launch_clustered(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, P.cluster, maps, mx, P);
+    if (rc || !partial || P.cluster > 1) return rc;
     return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + kReduceCols - 1) / kReduceCols), dim3(256), 0, stream, who, P, grid);
 }
 
@@ -892,11 +1046,7 @@ static int noalloc_setup(NoAllocState& out, const char* who)
         if (rc) return rc;
         rc = check_cuda(cudaGetSymbolAddress((void**)&status, g_noalloc_status), who);
         if (rc) return rc;
-        cudaFuncAttributes fa;
-        rc = check_cuda(cudaFuncGetAttributes(&fa, gemm_tc_kernel), who);
-        if (rc) return rc;
-        rc = check_cuda(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             227 * 1024 - (int)fa.sharedSizeBytes), who);
+        rc = ensure_smem_attr(who);
         if (rc) return rc;
         st.ws = ws; st.status = status; st.ready = true;
     }
@@ -947,7 +1097,7 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(P, grid, c).hi % P.KB != 0;
 
     const size_t smem = gemm_smem_bytes(P.BN);
-    rc = launch(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, maps, mx, P);
-    if (rc || !partial) return rc;
+    rc = launch_clustered(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, P.cluster, maps, mx, P);
+    if (rc || !partial || P.cluster > 1) return rc;
     return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + kReduceCols - 1) / kReduceCols), dim3(256), 0, stream, who, P, grid);
 }
