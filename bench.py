@@ -44,6 +44,10 @@ WORKLOADS = {
 }
 
 
+# (dram read + write) / packed bytes measured with ncu, per dominant kernel
+TRAFFIC_RATIO = {"gemv_stream_kernel": 1.022, "gemm_tc_kernel": 1.154}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -352,7 +356,12 @@ def run_ours(args):
         roof = {"bound": "hbm", "achieved": round(per_gpu_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
                 "frac": round(per_gpu_gbs / hbm_peak, 4), "traffic": None}
     roof["peak_source"] = f"{peak_src} (MEASURED_PEAKS.json)" if peak_src == "measured" else "fallback"
-    roof["kernel"] = "gemv_stream_kernel" if B == 1 else "gemm"
+    roof["kernel"] = "gemv_stream_kernel" if B == 1 else ("gemm_tc_kernel" if B > 16 else "gemv_kernel")
+    # DRAM bytes (read + write) per step and GPU: ncu captures of a one-layer run of the same workload
+    # (summaries under profiles/) gave this ratio to the packed bytes; traffic grows with the layer count.
+    ratio = TRAFFIC_RATIO.get(roof["kernel"])
+    roof["traffic"] = int(total_bytes / world * ratio) if ratio else None
+    roof["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum on a one-layer run, scaled by packed bytes" if ratio else None
     roof["algorithmic_bytes_per_step"] = int(total_bytes)
 
     line = {
