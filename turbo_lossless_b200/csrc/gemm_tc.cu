@@ -25,9 +25,10 @@
 // Work is split stream-K style: the (M tiles x N tiles x 256-column blocks) iteration
 // space is cut into equal contiguous ranges, one per CTA, so a 4096-row
 // projection (32 tiles) still occupies all 148 SMs.  A CTA that covers only
-// part of a tile's K range writes its partial accumulator to a workspace and
-// gemm_reduce_kernel adds the partials of each such tile in CTA order, so the
-// output is deterministic.
+// part of a tile's K range and does not hold the tile's first iteration writes
+// its partial accumulator to a workspace; the CTA that does hold it adds those
+// partials to its own while it drains, in CTA order, so the output is
+// deterministic.  Shapes with few tiles use thread-block clusters instead (below).
 //
 // Escapes: with the CSR list the decoded weights are exact inside the MMA;
 // without it they keep the reference's "wrong" value (exponent base_exp), which
@@ -98,7 +99,8 @@ struct GemmTensor {
 struct GemmParams {
     GemmTensor t[kMaxGemmTensors];
     int nt;
-    float* ws;                  // [grid][2][BN][kTileRows] partial accumulators
+    float* ws;                  // [grid][BN][kTileRows] partial accumulators, one slot per CTA
+    unsigned int* flags;        // [grid] hand-over counters of the partial slots (zero between launches)
     unsigned int* status;
     int K, B;
     int BN;                     // sequences per tile (multiple of 16, <= 256)
@@ -329,36 +331,104 @@ __device__ __forceinline__ void decode_row(const uint8_t* raw, int r, int sub, u
     }
 }
 
-// Moves 32-column chunks first, first+step, ... of a finished accumulator from
-// tensor memory to their destination: the output when the segment covered the
-// tile's whole K range, else this CTA's partial-tile slot of the workspace.
-// The calling thread owns accumulator row `mrow` (tensor-memory lane).
-__device__ __forceinline__ void drain_chunks(const GemmParams& P, const GemmTensor& T, uint32_t tmem_acc, int first, int step,
-                                             bool whole, int m, int mrow, int b0, float* wsp)
+// A tile whose K range is shared by several CTAs (stream-K) is finished by its
+// owner, the CTA whose range holds the tile's first iteration.  The others
+// ("contributors") meet the tile in the FIRST segment of their ranges, so their
+// partial accumulators are in the workspace long before the owner reaches the
+// tile at the END of its range; the owner adds them to its own accumulator while
+// it drains (own part first, then the contributors in CTA order: deterministic)
+// and stores the result.  No second kernel and one partial slot per CTA.
+// Hand-over counter of a slot: each of the W draining warps of the contributor
+// adds 1 after its stores (0 -> W), each of the W draining warps of the owner
+// adds 1 when it has read the slot (W -> 2W), and the last of them sets it back
+// to 0 for the next launch.
+enum DrainKind { kDrainWhole = 0, kDrainContributor = 1, kDrainOwner = 2 };
+
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p)
 {
-    const int BN = P.BN;
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// How many CTAs after this one also work on the tile that ends at iteration tile_end.
+__device__ __noinline__ int count_contributors(const GemmParams& P, int tile_end)
+{
+    int n = 0;
+    for (int c = (int)blockIdx.x + 1; c < (int)gridDim.x && cta_range(P, gridDim.x, c).lo < tile_end; c++) n++;
+    return n;
+}
+
+// Moves 32-column chunks first, first+step, ... of a finished accumulator from
+// tensor memory to their destination: the output (whole tile, or owner after
+// adding the contributors' partials) or this CTA's partial slot (contributor).
+// Called by whole warps; W = number of warps that drain a segment.  The calling
+// thread owns accumulator row `mrow` (tensor-memory lane).
+__device__ __forceinline__ void drain_chunks(const GemmParams& P, const GemmTensor& T, uint32_t tmem_acc, int first, int step,
+                                             int kind, int ncontrib, int W, int m, int mrow, int b0, int* s_abort)
+{
+    const int BN = P.BN, lane = threadIdx.x & 31;
+    const size_t slot = (size_t)BN * kTileRows;
+    if (kind == kDrainOwner) {
+        if (lane == 0) {
+            for (int ci = 1; ci <= ncontrib; ci++) {
+                const unsigned int* f = P.flags + blockIdx.x + ci;
+                unsigned int spins = 0;
+                while (ld_acquire_u32(f) < (unsigned)W) {
+                    if (*(volatile int*)s_abort || ++spins > (1u << 22)) {   // ~2 s: give up, flag the launch
+                        atomicOr(P.status, 0x4000u);
+                        *(volatile int*)s_abort = 1;
+                        break;
+                    }
+                    __nanosleep(256);
+                }
+            }
+        }
+        __syncwarp();
+    }
     for (int c0 = first * 32; c0 < BN; c0 += step * 32) {
         uint32_t v[32];
         tmem_ld32(tmem_acc + (uint32_t)c0, v);
         tmem_ld_wait();
-        if (whole) {
-            if (m < T.M) {
-                float* o = T.out + (size_t)(b0 + c0) * T.out_stride + m;
-                if (b0 + c0 + 32 <= P.B) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) o[(size_t)j * T.out_stride] = __uint_as_float(v[j]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (b0 + c0 + j < P.B) o[(size_t)j * T.out_stride] = __uint_as_float(v[j]);
-                }
-            }
-        } else {
-            float* o = wsp + (size_t)c0 * kTileRows + mrow;
+        if (kind == kDrainContributor) {
+            float* o = P.ws + blockIdx.x * slot + (size_t)c0 * kTileRows + mrow;
 #pragma unroll
             for (int j = 0; j < 32; j++)
                 if (c0 + j < BN) o[j * kTileRows] = __uint_as_float(v[j]);
+            continue;
         }
+        for (int ci = 1; ci <= ncontrib; ci++) {                  // owner only (ncontrib is 0 for whole tiles)
+            const float* pp = P.ws + (blockIdx.x + ci) * slot + (size_t)c0 * kTileRows + mrow;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float part[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) part[j] = (c0 + h * 16 + j < BN) ? __ldcg(pp + (h * 16 + j) * kTileRows) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; j++) v[h * 16 + j] = __float_as_uint(__uint_as_float(v[h * 16 + j]) + part[j]);
+            }
+        }
+        if (m < T.M) {
+            float* o = T.out + (size_t)(b0 + c0) * T.out_stride + m;
+            if (b0 + c0 + 32 <= P.B) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) o[(size_t)j * T.out_stride] = __uint_as_float(v[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (b0 + c0 + j < P.B) o[(size_t)j * T.out_stride] = __uint_as_float(v[j]);
+            }
+        }
+    }
+    if (kind == kDrainContributor) {
+        __threadfence();                                          // the partials before the counter
+        __syncwarp();
+        if (lane == 0) atomicAdd(P.flags + blockIdx.x, 1u);
+    } else if (kind == kDrainOwner) {
+        __syncwarp();
+        if (lane == 0)
+            for (int ci = 1; ci <= ncontrib; ci++)
+                if (atomicAdd(P.flags + blockIdx.x + ci, 1u) == (unsigned)(2 * W - 1)) atomicExch(P.flags + blockIdx.x + ci, 0u);
     }
 }
 
@@ -621,9 +691,10 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
                     tc_fence_after();
                     grid_dependency_wait();                       // the output buffer may still be in use
                     const int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
-                    float* wsp = P.ws + ((size_t)blockIdx.x * 2 + (nacc == 0 ? 0 : 1)) * (size_t)BN * kTileRows;
-                    drain_chunks(P, T, tmem_base + ((uint32_t)((t >> 5) * 32) << 16), gi + 1, kDrainTeams,
-                                 seg_kb0 == 0 && kb + 1 == KB, tr.mt * kTileRows + t, t, nt * BN, wsp);
+                    const int kind = seg_kb0 != 0 ? kDrainContributor : (kb + 1 == KB ? kDrainWhole : kDrainOwner);
+                    const int ncontrib = kind == kDrainOwner ? count_contributors(P, (tile + 1) * KB) : 0;
+                    drain_chunks(P, T, tmem_base + ((uint32_t)((t >> 5) * 32) << 16), gi + 1, kDrainTeams, kind, ncontrib,
+                                 4 + kDecodeWarps, tr.mt * kTileRows + t, t, nt * BN, &s_abort);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(b_accempty);
@@ -648,7 +719,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
         while (it < rg.hi) {
             const int tile_lo = tile * KB, tile_end = tile_lo + KB;
             const int seg_end = tile_end < rg.hi ? tile_end : rg.hi;
-            const bool whole = it == tile_lo && seg_end == tile_end;
+            const int kind = it != tile_lo ? kDrainContributor : (seg_end == tile_end ? kDrainWhole : kDrainOwner);
+            const int ncontrib = kind == kDrainOwner ? count_contributors(P, tile_end) : 0;
             const int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
             const TileRef tr = locate_mtile(P, mtg);
             const GemmTensor& T = P.t[tr.ti];
@@ -658,12 +730,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             tc_fence_after();
             const int b0 = nt * BN;
             const int m = tr.mt * kTileRows + mrow;
-            // A segment that covers only part of its tile's K range goes to the
-            // workspace (slot 0: the tile this CTA's range starts in, slot 1: the
-            // tile it ends in) and is summed by gemm_reduce_kernel.
-            float* wsp = P.ws + ((size_t)blockIdx.x * 2 + (it == rg.lo ? 0 : 1)) * (size_t)BN * kTileRows;
             drain_chunks(P, T, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN), 0, two_acc ? 1 : kDrainTeams,
-                         whole, m, mrow, b0, wsp);
+                         kind, ncontrib, two_acc ? 4 : 4 + kDecodeWarps, m, mrow, b0, &s_abort);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(b_accempty + 8 * buf);     // accumulator may be overwritten
@@ -680,75 +748,6 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
     if (threadIdx.x == 0) GP(5);
-}
-
-// Sums the partial accumulators of every tile whose K range was shared by
-// several CTAs, in CTA order (deterministic), and stores the result.  One CTA
-// per (range boundary, 32-sequence slab); boundaries that cut no tile exit at
-// once.
-constexpr int kReduceCols = 32;                                  // sequences per CTA of the fix-up pass
-__global__ void __launch_bounds__(256)
-gemm_reduce_kernel(const __grid_constant__ GemmParams P, int G)
-{
-    grid_launch_dependents();
-    grid_dependency_wait();
-#ifdef S12_GEMM_TRACE
-    if (threadIdx.x == 0) atomicMin(&g_gphase[160][0], gt_now());
-    struct AtExit { __device__ ~AtExit() { if (threadIdx.x == 0) atomicMax(&g_gphase[160][1], gt_now()); } } at_exit;
-#endif
-    // CTA c looks at the end of GEMM CTA c's range: if it cuts a tile and c is the first CTA
-    // working on that tile, this CTA sums the tile's partials
-    const int KB = P.KB, BN = P.BN;
-    const int c_first = blockIdx.x;
-    const Range r0 = cta_range(P, G, c_first);
-    if (r0.hi % KB == 0) return;
-    const int tile = r0.hi / KB, tile_lo = tile * KB, tile_end = tile_lo + KB;
-    if (r0.lo > tile_lo) return;
-    int c_last = c_first + 1;
-    while (c_last + 1 < G && cta_range(P, G, c_last + 1).lo < tile_end) c_last++;
-    const int nparts = c_last - c_first + 1;
-    __shared__ const float* s_part[192];
-    for (int i = threadIdx.x; i < nparts; i += blockDim.x) {
-        const int c = c_first + i;
-        const int slot = cta_range(P, G, c).lo >= tile_lo ? 0 : 1;
-        s_part[i] = P.ws + ((size_t)c * 2 + slot) * (size_t)BN * kTileRows;
-    }
-    __syncthreads();
-    const int mtg = tile / P.n_ntiles, nt = tile - mtg * P.n_ntiles;
-    const TileRef tr = locate_mtile(P, mtg);
-    const GemmTensor& W = P.t[tr.ti];
-    const int mt = tr.mt;
-    constexpr int kRowLanes = kTileRows / 4;                     // threads across the rows of a tile
-    const int m4 = (threadIdx.x % kRowLanes) * 4;                // four consecutive rows per thread
-    const int b0 = nt * BN;
-    for (int j = blockIdx.y * kReduceCols + threadIdx.x / kRowLanes; j < (blockIdx.y + 1) * kReduceCols && j < BN;
-         j += 256 / kRowLanes) {
-        if (b0 + j >= P.B) break;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        const size_t off = (size_t)j * kTileRows + m4;
-        int i = 0;
-        for (; i + 4 <= nparts; i += 4) {                        // four loads in flight, summed in CTA order
-            float4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) v[u] = __ldcg(reinterpret_cast<const float4*>(s_part[i + u] + off));
-#pragma unroll
-            for (int u = 0; u < 4; u++) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
-        }
-        for (; i < nparts; i++) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(s_part[i] + off));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
-        const int m = mt * kTileRows + m4;
-        float* dst = W.out + (size_t)(b0 + j) * W.out_stride + m;
-        if (m + 3 < W.M && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-            *reinterpret_cast<float4*>(dst) = acc;
-        } else {
-            if (m < W.M) dst[0] = acc.x;
-            if (m + 1 < W.M) dst[1] = acc.y;
-            if (m + 2 < W.M) dst[2] = acc.z;
-            if (m + 3 < W.M) dst[3] = acc.w;
-        }
-    }
 }
 
 // ----------------------------------------------------------------------------
@@ -792,8 +791,10 @@ static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, u
 }
 
 // Per-device workspace for partial accumulators (grow-only, allocated on first
-// use or when a larger one is needed).
-struct Scratch { float* ws = nullptr; size_t ws_bytes = 0; };
+// use or when a larger one is needed), followed by the hand-over counters of
+// the slots, which start at zero and are left at zero by every launch.
+constexpr size_t kFlagBytes = 4096;                              // room for 1024 CTAs
+struct Scratch { float* ws = nullptr; unsigned int* flags = nullptr; size_t ws_bytes = 0; };
 static Scratch g_scratch[64];
 static std::mutex g_scratch_mu;
 
@@ -808,7 +809,10 @@ static int get_scratch(size_t ws_bytes, Scratch& out, const char* who)
         cudaDeviceSynchronize();
         if (s.ws) cudaFree(s.ws);
         s.ws = nullptr; s.ws_bytes = 0;
-        int rc = check_cuda(cudaMalloc(&s.ws, ws_bytes), who);
+        int rc = check_cuda(cudaMalloc(&s.ws, ws_bytes + kFlagBytes), who);
+        if (rc) return rc;
+        s.flags = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(s.ws) + ws_bytes);
+        rc = check_cuda(cudaMemset(s.flags, 0, kFlagBytes), who);
         if (rc) return rc;
         s.ws_bytes = ws_bytes;
     }
@@ -919,13 +923,13 @@ static int gemm_env_int(const char* name, int dflt)
 // Picks how the iteration space is cut (P.split) and the number of CTAs, at most
 // max_grid, by a small cost model in microseconds whose constants were measured
 // on this kernel: a raw stage takes ~1.25 us, every tile segment of a CTA costs
-// ~3 us of pipeline drain and refill, and the fix-up pass costs its launch plus
-// reading the partial tiles (which mostly still sit in L2).
+// ~3 us of pipeline drain and refill, and the stream-K hand-over of partial
+// tiles costs ~6 us at the end of the owners' ranges.
 static int choose_schedule(GemmParams& P, int max_grid)
 {
     const long long tiles = (long long)P.n_mtiles * P.n_ntiles, T = tiles * P.KB;
-    const double tb = 1.25, seg = 3.0, tile_mb = (double)P.BN * kTileRows * 4 / 1e6;
-    auto fixup = [&](double nparts) { return 2.5 + nparts * tile_mb / 5.5; };
+    const double tb = 1.25, seg = 3.0;
+    auto fixup = [&](double) { return 6.0; };                    // owners add the partials at the very end of their ranges
     // stream-K, never finer than 2 raw stages per CTA
     int best_grid = (int)std::min<long long>(max_grid, std::max<long long>(1, T / 2));
     int best_split = 0;
@@ -980,17 +984,12 @@ int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_st
     if (rc) return rc;
     const int grid = choose_schedule(P, sms);
     Scratch sc;
-    rc = get_scratch((size_t)sms * 2 * 256 * kTileRows * sizeof(float), sc, who);   // sized for the largest launch
+    rc = get_scratch((size_t)sms * 256 * kTileRows * sizeof(float), sc, who);      // one slot per CTA, largest launch
     if (rc) return rc;
     P.ws = sc.ws;
-    // does any tile have its K range shared between CTAs?
-    bool partial = false;
-    for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(P, grid, c).hi % P.KB != 0;
-
+    P.flags = sc.flags;
     const size_t smem = gemm_smem_bytes(P.BN);
-    rc = launch_clustered(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, P.cluster, maps, mx, P);
-    if (rc || !partial || P.cluster > 1) return rc;
-    return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + kReduceCols - 1) / kReduceCols), dim3(256), 0, stream, who, P, grid);
+    return launch_clustered(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, P.cluster, maps, mx, P);
 }
 
 int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
@@ -1023,8 +1022,9 @@ constexpr int kNoAllocMaxB = 256;                                  // one tile o
 
 static __device__ __align__(256) float g_noalloc_ws[kNoAllocWsFloats];
 static __device__ unsigned int g_noalloc_status;
+static __device__ unsigned int g_noalloc_flags[256];               // hand-over counters, zero between launches
 
-struct NoAllocState { float* ws; unsigned int* status; bool ready; };
+struct NoAllocState { float* ws; unsigned int* status; unsigned int* flags; bool ready; };
 static NoAllocState g_noalloc[64];
 static std::mutex g_noalloc_mu;
 
@@ -1046,9 +1046,12 @@ static int noalloc_setup(NoAllocState& out, const char* who)
         if (rc) return rc;
         rc = check_cuda(cudaGetSymbolAddress((void**)&status, g_noalloc_status), who);
         if (rc) return rc;
+        unsigned int* flags = nullptr;
+        rc = check_cuda(cudaGetSymbolAddress((void**)&flags, g_noalloc_flags), who);
+        if (rc) return rc;
         rc = ensure_smem_attr(who);
         if (rc) return rc;
-        st.ws = ws; st.status = status; st.ready = true;
+        st.ws = ws; st.status = status; st.flags = flags; st.ready = true;
     }
     out = st;
     return S12_OK;
@@ -1086,18 +1089,14 @@ extern "C" int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int a
     if (rc) return rc;
     P.status = st.status;
     P.ws = st.ws;
+    P.flags = st.flags;
     const long long T = (long long)P.n_mtiles * P.KB;
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: M*K exceeds the tile schedule's range", who);
 
-    // CTAs: as the regular path, then capped so that two partial tiles per CTA fit the fixed scratch
-    const size_t per_cta = (size_t)2 * P.BN * kTileRows;
-    const int fit = (int)(kNoAllocWsFloats / per_cta);
+    // CTAs: as the regular path, then capped so that one partial tile per CTA fits the fixed scratch
+    const size_t per_cta = (size_t)P.BN * kTileRows;
+    const int fit = (int)std::min<size_t>(kNoAllocWsFloats / per_cta, 256);
     const int grid = choose_schedule(P, std::max(1, std::min(sm_count(), fit)));
-    bool partial = false;
-    for (int c = 0; c + 1 < grid && !partial; c++) partial = cta_range(P, grid, c).hi % P.KB != 0;
-
     const size_t smem = gemm_smem_bytes(P.BN);
-    rc = launch_clustered(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, P.cluster, maps, mx, P);
-    if (rc || !partial || P.cluster > 1) return rc;
-    return launch(gemm_reduce_kernel, dim3(grid - 1, (P.BN + kReduceCols - 1) / kReduceCols), dim3(256), 0, stream, who, P, grid);
+    return launch_clustered(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, P.cluster, maps, mx, P);
 }
