@@ -59,6 +59,9 @@ def parse_args():
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (development only)")
+    ap.add_argument("--comm", default="own", choices=["own", "nccl"],
+                    help="all-reduce after the row-parallel projections at N > 1: this library's one-shot kernel over "
+                         "peer memory (inside the step's CUDA graph) or NCCL called between graph segments")
     return ap.parse_args()
 
 
@@ -172,7 +175,7 @@ def _log(msg):
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from turbo_lossless_b200 import CompressedWeight, Split12Engine
+    from turbo_lossless_b200 import CompressedWeight, Split12Engine, TPComm
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -184,6 +187,7 @@ def run_ours(args):
     layers = args.layers or cfg["layers"]
     B, H, V = cfg["batch"], cfg["hidden"], cfg["vocab"]
     eng = Split12Engine()
+    comm = TPComm(rank, world, B * H) if (world > 1 and args.comm == "own") else None
     _log("process group up; building model")
     model = build_model(cfg, rank, world, layers, torch, CompressedWeight)
     _log("model packed")
@@ -227,10 +231,20 @@ def run_ours(args):
             launches[0] += 1
 
     # The step as a list of segments: ("k", fn) = our launches only (capturable as one CUDA graph),
-    # ("ar", tensor) = the all-reduce after a row-parallel projection.  NCCL collectives are kept
-    # out of graph capture (capturing them hung on this pool), so with N > 1 a step replays one
-    # small graph per segment and calls all_reduce between them.
+    # ("ar", tensor) = an NCCL all-reduce after a row-parallel projection.  With --comm own (default) the
+    # all-reduce is a kernel of this library and the whole step stays one graph.  NCCL collectives are
+    # kept out of graph capture (capturing them hung on this pool), so with --comm nccl a step replays
+    # one small graph per segment and calls all_reduce between them.
     segments = []
+
+    def all_reduce(t):
+        if comm is not None:
+            def ar(t=t):
+                comm.all_reduce(t)
+                launches[0] += 1
+            add_k(ar)
+        else:
+            segments.append(("ar", t))
 
     def add_k(fn):
         if segments and segments[-1][0] == "k":
@@ -244,14 +258,14 @@ def run_ours(args):
             add_k(lambda L=L: proj([L["wq"], L["wk"], L["wv"]], x_hidden, [o_q, o_k, o_v]))
             add_k(lambda L=L: proj([L["wo"]], x_attn, [o_o]))
             if world > 1:
-                segments.append(("ar", o_o))
+                all_reduce(o_o)
         else:
             add_k(lambda L=L: proj([L["wq"]], x_hidden, [o_q]))
         if "w_gate" in L:
             add_k(lambda L=L: proj([L["w_gate"], L["w_up"]], x_hidden, [o_g, o_u]))
             add_k(lambda L=L: proj([L["w_down"]], x_ffn, [o_d]))
             if world > 1:
-                segments.append(("ar", o_d))
+                all_reduce(o_d)
     if model["lm_head"] is not None:
         add_k(lambda: proj([model["lm_head"]], x_hidden, [logits]))
 
@@ -371,6 +385,9 @@ def run_ours(args):
         "data": "synthetic: seeded N(0,0.02) bf16 weights packed to split12 on the device; random bf16 activations",
         "config": {"workload": args.workload, "what": cfg["desc"], "layers": layers, "batch": B,
                    "parallelism": f"tp{world}" if world > 1 else "single",
+                   "collective": ("none" if world == 1 else
+                                  "one-shot all-reduce kernel over NVLink peer memory, inside the step's graph" if comm is not None
+                                  else "NCCL all_reduce between graph segments"),
                    "l2": "inputs larger than L2 (packed weights of one step: %.2f GB per GPU)" % (total_bytes / world / 1e9),
                    "launch": ("cuda graph" if graph is not None else "eager") + ("" if args.no_pdl else " + programmatic dependent launch"),
                    "excluded": "norm/rope/attention/sampling kernels between the projections are not part of this path"},

@@ -210,8 +210,10 @@ int s12_gemm_multi_async(const S12Tensor* w, int num_tensors, const void* act, i
  * device address (cudaGetSymbolAddress) and sets a kernel attribute; make that
  * first call before any stream capture.  All calls on a device share the one
  * array: calls whose kernels may overlap on the GPU (different streams) race
- * on it and must be serialised by the caller.  Nothing in the array needs to
- * start at zero: every partial is written before it is read in the same call. */
+ * on it and must be serialised by the caller.  Nothing in the 8 MiB array
+ * needs to start at zero (every partial is written before it is read in the
+ * same call); the hand-over counters of the partials sit in a second, 1 KB
+ * static array that starts at zero and is left at zero by every call. */
 int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int act_stride,
                            void* out, int out_stride, int B, void* stream);
 
@@ -279,6 +281,42 @@ int s12_pack_async(const void* bf16, int M, int K, int base_exp, void* sm, void*
  * column order within each row. */
 int s12_pack_fill_async(const void* bf16, int M, int K, int base_exp, const void* row_off,
                         void* cols, void* correct, void* wrong, void* stream);
+
+/* --------------------------------------------------------------------------
+ * Tensor parallelism: all-reduce after the row-parallel projections
+ * --------------------------------------------------------------------------
+ * No counterpart in the reference, which runs on one GPU.  When o / down are
+ * split by columns across GPUs (s12_host_shard_cols), each GPU holds a partial
+ * fp32 [B][hidden] result and the sum over GPUs is needed.  These calls do that
+ * sum with one kernel over NVLink peer memory (plain peer stores and loads), so
+ * that a whole decode step, collectives included, can be one CUDA graph.
+ * One process per GPU; the caller moves the opaque handles between processes
+ * with whatever it already has (e.g. an all-gather of bytes in its process
+ * group).  Device-side waits are bounded: a rank whose peers never arrive sets
+ * bit 0x8000 of the device status word (s12_device_status) and returns. */
+typedef struct S12Comm S12Comm;
+
+/* size of one handle (bytes) */
+int s12_comm_handle_bytes(void);
+/* Allocates this rank's receive area for vectors of up to max_floats floats on
+ * the current device and writes its handle to handle_out (may be null when the
+ * ranks share a process, see s12_comm_connect_local). */
+int s12_comm_create(int rank, int world, long long max_floats, S12Comm** out, void* handle_out);
+/* all_handles: the world handles in rank order (own entry ignored). */
+int s12_comm_connect(S12Comm* comm, const void* all_handles);
+/* out[i] = sum over ranks of in[i], i < n, added in rank order (bit-identical
+ * on every rank).  n: multiple of 4, <= max_floats.  in/out: device pointers,
+ * 16-byte aligned, may alias.  Every rank must issue the same sequence of
+ * calls with the same n.  Asynchronous on `stream`; capturable. */
+int s12_allreduce_f32_async(S12Comm* comm, const void* in, void* out, int n, void* stream);
+int s12_comm_destroy(S12Comm* comm);
+/* Test support for a single GPU: `world` communicators created in one process
+ * on one device are wired to each other, and one cooperative launch runs all
+ * ranks of a call side by side (ranks that wait on one another must never be
+ * separate launches on one GPU). */
+int s12_comm_connect_local(S12Comm* const* comms, int world);
+int s12_allreduce_f32_emulated_async(S12Comm* const* comms, int world, const void* const* ins,
+                                     void* const* outs, int n, void* stream);
 
 #ifdef __cplusplus
 }

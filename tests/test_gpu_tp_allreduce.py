@@ -1,0 +1,102 @@
+"""The tensor-parallel all-reduce kernel (s12_allreduce_f32_async).
+
+On one GPU the ranks of a call run as one cooperative launch (ranks that wait on one another are
+never separate launches on one device); with two or more GPUs the real path runs as one process
+per GPU with the IPC handles exchanged over a gloo group.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("n", [4, 4096, 14336, 65536 + 8])
+def test_emulated_ranks_one_launch(world, n):
+    import torch
+    from turbo_lossless_b200 import TPComm, Split12Engine
+    eng = Split12Engine()
+    comms = TPComm.local(world, 70000)
+    rng = np.random.default_rng(world * 1000 + n)
+    for call in range(3):                      # consecutive calls alternate the receive areas
+        parts = [rng.standard_normal(n).astype(np.float32) for _ in range(world)]
+        srcs = [torch.from_numpy(p).cuda() for p in parts]
+        dsts = [torch.full((n,), float("nan"), device="cuda") for _ in range(world)]
+        TPComm.all_reduce_emulated(comms, srcs, dsts)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        ref = np.zeros(n, dtype=np.float32)
+        for p in parts:                        # rank order, fp32: the kernel's order of additions
+            ref = ref + p
+        for d in dsts:
+            np.testing.assert_array_equal(d.cpu().numpy(), ref)
+    for c in comms:
+        c.close()
+
+
+def test_rejects_bad_sizes():
+    import torch
+    from turbo_lossless_b200 import TPComm, S12Error
+    (c,) = TPComm.local(1, 1024)
+    x = torch.zeros(2048, device="cuda")
+    with pytest.raises(S12Error):
+        c.all_reduce(x)                        # beyond the capacity
+    with pytest.raises(S12Error):
+        c.all_reduce(x[:6])                    # not a multiple of 4
+    y = torch.arange(1024, device="cuda", dtype=torch.float32)
+    out = c.all_reduce(y.clone())              # world of one: identity
+    torch.cuda.synchronize()
+    assert torch.equal(out, y)
+    c.close()
+
+
+_WORKER = r"""
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("gloo", rank=rank, world_size=world)
+from turbo_lossless_b200 import TPComm, Split12Engine
+eng = Split12Engine()
+comm = TPComm(rank, world, 1 << 20)
+ok = True
+for call, n in enumerate([4096, 4096, 14336, 1 << 20, 4096]):
+    parts = [np.random.default_rng(100 * call + r).standard_normal(n).astype(np.float32) for r in range(world)]
+    x = torch.from_numpy(parts[rank]).cuda()
+    out = torch.empty_like(x)
+    comm.all_reduce(x, out)
+    torch.cuda.synchronize()
+    ref = np.zeros(n, dtype=np.float32)
+    for p in parts:
+        ref = ref + p
+    ok = ok and np.array_equal(out.cpu().numpy(), ref) and eng.device_status() == 0
+dist.barrier()
+comm.close()
+dist.destroy_process_group()
+sys.exit(0 if ok else 1)
+"""
+
+
+def test_two_processes_two_gpus(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29533",
+                   PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env))
+    try:
+        codes = [p.wait(timeout=120) for p in procs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    assert codes == [0, 0]

@@ -7,6 +7,6 @@ host-side structures so that tests and benchmarks read like the engine's call
 sites; all arithmetic of the path runs in the CUDA library.
 """
 from .capi import S12Error, S12Tensor, load  # noqa: F401
-from .engine import CompressedWeight, Split12Engine  # noqa: F401
+from .engine import CompressedWeight, Split12Engine, TPComm  # noqa: F401
 
-__all__ = ["S12Error", "S12Tensor", "load", "CompressedWeight", "Split12Engine"]
+__all__ = ["S12Error", "S12Tensor", "load", "CompressedWeight", "Split12Engine", "TPComm"]

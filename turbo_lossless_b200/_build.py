@@ -8,7 +8,7 @@ import sys
 _PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_PATH = os.path.join(_PKG, "libsplit12_b200.so")
-SOURCES = ["runtime.cu", "decompress.cu", "patches.cu", "gemv.cu", "gemv_stream.cu", "gemm.cu", "gemm_tc.cu", "pack.cu", "host.cpp"]
+SOURCES = ["runtime.cu", "decompress.cu", "patches.cu", "gemv.cu", "gemv_stream.cu", "gemm.cu", "gemm_tc.cu", "pack.cu", "comm.cu", "host.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--use_fast_math"]
 

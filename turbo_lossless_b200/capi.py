@@ -58,6 +58,13 @@ SIGNATURES = {
     "s12_pack_find_base_exp_host": (_i, [_vp]),
     "s12_pack_async": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "s12_pack_fill_async": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "s12_comm_handle_bytes": (_i, []),
+    "s12_comm_create": (_i, [_i, _i, C.c_longlong, C.POINTER(_vp), _vp]),
+    "s12_comm_connect": (_i, [_vp, _vp]),
+    "s12_comm_connect_local": (_i, [C.POINTER(_vp), _i]),
+    "s12_allreduce_f32_async": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "s12_allreduce_f32_emulated_async": (_i, [C.POINTER(_vp), _i, C.POINTER(_vp), C.POINTER(_vp), _i, _vp]),
+    "s12_comm_destroy": (_i, [_vp]),
 }
 
 _lib = None

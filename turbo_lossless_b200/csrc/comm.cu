@@ -1,0 +1,280 @@
+// Tensor-parallel all-reduce of the row-parallel projections' fp32 results over
+// NVLink peer memory, as one kernel that can sit inside a CUDA graph.
+//
+// The reference has no multi-GPU path; this is the collective that follows the
+// row-parallel GEMV/GEMM (o and down projections) when a model's weights are
+// sharded across GPUs.  One process per GPU.  Every rank owns a receive area in
+// its own memory that all ranks can address (CUDA IPC; the handles travel
+// through the caller's process group):
+//
+//   recv  [2 parities][world][capacity] fp32   partial vectors, one row per source rank
+//   flags [2 parities][kMaxCtas][world] u32    arrival tokens, one per (CTA, source rank)
+//
+// One-shot algorithm, per CTA on its own slice of the vector (so no grid-wide
+// step exists): push the slice into every rank's recv[parity][my rank], fence,
+// store the call's token into every rank's flag for (this CTA, my rank); wait
+// (bounded) until the tokens of all source ranks have arrived here; add the
+// world partials in rank order (every rank gets bit-identical sums) and store.
+// Consecutive calls alternate between the two parities: a rank can be at most
+// one call ahead of a peer, because finishing call k needs the peer's data of
+// call k, so two areas are enough.  The call counter lives in device memory
+// (one per CTA), which makes the kernel replayable from a CUDA graph.
+//
+// Plain peer stores and loads only: no multimem, no TMA.
+#include "common.cuh"
+#include <mutex>
+#include <vector>
+
+namespace s12 {
+
+constexpr int kCommMaxWorld = 8;
+constexpr int kCommMaxCtas = 64;
+constexpr int kCommThreads = 512;
+constexpr int kCommMinSlice = 2048;          // floats per CTA before another CTA is added
+
+struct CommRank {
+    float* recv[kCommMaxWorld];              // every rank's receive area (index = owner rank), as mapped here
+    unsigned int* flags[kCommMaxWorld];      // every rank's flag area
+    unsigned int* seq;                       // [kMaxCtas] calls completed, local
+    unsigned int* status;                    // local status word (bit 0x8000: a wait gave up)
+    int rank;
+};
+
+struct AllReduceParams {
+    CommRank r[kCommMaxWorld];               // [0] in a real launch; [y] when several ranks are emulated in one launch
+    const float* in[kCommMaxWorld];
+    float* out[kCommMaxWorld];
+    int world, capacity, n;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(kCommThreads)
+allreduce_kernel(const __grid_constant__ AllReduceParams P)
+{
+    const CommRank& R = P.r[blockIdx.y];
+    const float* in = P.in[blockIdx.y];
+    float* out = P.out[blockIdx.y];
+    const int world = P.world, me = R.rank, cta = blockIdx.x;
+    __shared__ unsigned int s_seq;
+    __shared__ int s_giveup;
+    grid_launch_dependents();
+    if (threadIdx.x == 0) { s_seq = R.seq[cta]; s_giveup = 0; }
+    __syncthreads();
+    const unsigned int token = s_seq + 1u;
+    const int parity = (int)(s_seq & 1u);
+
+    // this CTA's slice, in float4 units
+    const int n4 = P.n >> 2;
+    const int lo = (int)((long long)n4 * cta / gridDim.x), hi = (int)((long long)n4 * (cta + 1) / gridDim.x);
+    const size_t row = (size_t)P.capacity;
+
+    grid_dependency_wait();                                       // `in` comes from the preceding kernel
+    // 1. push my partial slice into every rank's receive row for me
+    for (int i = lo + threadIdx.x; i < hi; i += kCommThreads) {
+        const float4 v = reinterpret_cast<const float4*>(in)[i];
+#pragma unroll 1
+        for (int p = 0; p < world; p++)
+            reinterpret_cast<float4*>(R.recv[p] + ((size_t)parity * world + me) * row)[i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    // 2. tell every rank that my slice has arrived
+    if ((int)threadIdx.x < world)
+        st_release_sys(R.flags[threadIdx.x] + ((size_t)parity * kCommMaxCtas + cta) * world + me, token);
+    // 3. wait for every rank's slice (bounded: about two seconds)
+    if ((int)threadIdx.x < world) {
+        const unsigned int* f = R.flags[me] + ((size_t)parity * kCommMaxCtas + cta) * world + threadIdx.x;
+        unsigned int spins = 0;
+        while ((int)(ld_acquire_sys(f) - token) < 0) {
+            if (++spins > (1u << 23)) { atomicOr(R.status, 0x8000u); s_giveup = 1; break; }
+            __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    // 4. add the partials in rank order
+    const float* mine = R.recv[me] + (size_t)parity * world * row;
+    for (int i = lo + threadIdx.x; i < hi; i += kCommThreads) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+        for (int p = 0; p < world; p++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(mine + p * row) + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        reinterpret_cast<float4*>(out)[i] = acc;
+    }
+    if (threadIdx.x == 0) R.seq[cta] = token;
+}
+
+}  // namespace s12
+
+// ----------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------
+struct S12Comm {
+    int rank = 0, world = 1, device = 0;
+    int capacity = 0;                         // floats per receive row
+    char* base = nullptr;                     // local allocation: recv area, then flag area
+    size_t recv_bytes = 0, flag_bytes = 0;
+    char* peer_base[s12::kCommMaxWorld] = {};  // every rank's allocation as mapped in this process
+    bool opened[s12::kCommMaxWorld] = {};      // mapped through an IPC handle (must be closed)
+    unsigned int* seq = nullptr;
+    bool connected = false;
+};
+
+extern "C" {
+
+int s12_comm_handle_bytes(void) { return (int)sizeof(cudaIpcMemHandle_t); }
+
+int s12_comm_create(int rank, int world, long long max_floats, S12Comm** out, void* handle_out)
+{
+    using namespace s12;
+    const char* who = "s12_comm_create";
+    if (!out || world < 1 || world > kCommMaxWorld || rank < 0 || rank >= world || max_floats < 4)
+        return fail(S12_ERR_BAD_ARG, "%s: need 0 <= rank < world <= %d, max_floats >= 4", who, kCommMaxWorld);
+    if (max_floats > (1ll << 28)) return fail(S12_ERR_TOO_LARGE, "%s: max_floats too large", who);
+    S12Comm* c = new S12Comm();
+    c->rank = rank; c->world = world;
+    c->capacity = (int)((max_floats + 3) & ~3ll);
+    int rc = check_cuda(cudaGetDevice(&c->device), who);
+    c->recv_bytes = (size_t)2 * world * c->capacity * sizeof(float);
+    c->recv_bytes = (c->recv_bytes + 255) & ~(size_t)255;
+    c->flag_bytes = (size_t)2 * kCommMaxCtas * world * sizeof(unsigned int);
+    if (!rc) rc = check_cuda(cudaMalloc(&c->base, c->recv_bytes + c->flag_bytes), who);
+    if (!rc) rc = check_cuda(cudaMemset(c->base, 0, c->recv_bytes + c->flag_bytes), who);
+    if (!rc) rc = check_cuda(cudaMalloc(&c->seq, kCommMaxCtas * sizeof(unsigned int)), who);
+    if (!rc) rc = check_cuda(cudaMemset(c->seq, 0, kCommMaxCtas * sizeof(unsigned int)), who);
+    if (!rc && handle_out) {
+        cudaIpcMemHandle_t h;
+        rc = check_cuda(cudaIpcGetMemHandle(&h, c->base), who);
+        if (!rc) memcpy(handle_out, &h, sizeof h);
+    }
+    if (!rc) rc = check_cuda(cudaDeviceSynchronize(), who);
+    if (rc) { if (c->base) cudaFree(c->base); if (c->seq) cudaFree(c->seq); delete c; return rc; }
+    c->peer_base[rank] = c->base;
+    *out = c;
+    return S12_OK;
+}
+
+// all_handles: world handles of s12_comm_handle_bytes() bytes each, in rank order (the own entry is ignored)
+int s12_comm_connect(S12Comm* c, const void* all_handles)
+{
+    using namespace s12;
+    const char* who = "s12_comm_connect";
+    if (!c || !all_handles) return fail(S12_ERR_BAD_ARG, "%s: null argument", who);
+    for (int p = 0; p < c->world; p++) {
+        if (p == c->rank || c->peer_base[p]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)all_handles + (size_t)p * sizeof h, sizeof h);
+        void* ptr = nullptr;
+        int rc = check_cuda(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), who);
+        if (rc) return rc;
+        c->peer_base[p] = (char*)ptr;
+        c->opened[p] = true;
+    }
+    c->connected = true;
+    return S12_OK;
+}
+
+// Several ranks living in one process on one device (tests): every rank's area is plain local memory.
+int s12_comm_connect_local(S12Comm* const* comms, int world)
+{
+    using namespace s12;
+    if (!comms || world < 1 || world > kCommMaxWorld) return fail(S12_ERR_BAD_ARG, "s12_comm_connect_local: bad argument");
+    for (int r = 0; r < world; r++) {
+        if (!comms[r] || comms[r]->world != world || comms[r]->rank != r || comms[r]->capacity != comms[0]->capacity)
+            return fail(S12_ERR_BAD_ARG, "s12_comm_connect_local: communicator %d does not match", r);
+    }
+    for (int r = 0; r < world; r++) {
+        for (int p = 0; p < world; p++) comms[r]->peer_base[p] = comms[p]->base;
+        comms[r]->connected = true;
+    }
+    return S12_OK;
+}
+
+static int fill_rank(const S12Comm* c, s12::CommRank& R)
+{
+    for (int p = 0; p < c->world; p++) {
+        R.recv[p] = reinterpret_cast<float*>(c->peer_base[p]);
+        R.flags[p] = reinterpret_cast<unsigned int*>(c->peer_base[p] + c->recv_bytes);
+    }
+    R.seq = c->seq;
+    R.status = s12::device_status_word();
+    R.rank = c->rank;
+    return R.status ? S12_OK : S12_ERR_CUDA;
+}
+
+static int comm_ctas(int n)
+{
+    int ctas = n / s12::kCommMinSlice;
+    return ctas < 1 ? 1 : (ctas > s12::kCommMaxCtas ? s12::kCommMaxCtas : ctas);
+}
+
+// out[i] = sum over ranks of in[i], i < n; n a multiple of 4, n <= capacity; in/out 16-byte aligned device
+// pointers (they may be the same buffer).  Every rank must make the same sequence of calls with the same n.
+int s12_allreduce_f32_async(S12Comm* c, const void* in, void* out, int n, void* stream)
+{
+    using namespace s12;
+    const char* who = "s12_allreduce_f32_async";
+    if (!c || !in || !out) return fail(S12_ERR_BAD_ARG, "%s: null argument", who);
+    if (!c->connected) return fail(S12_ERR_BAD_ARG, "%s: communicator not connected", who);
+    if (n < 4 || (n & 3)) return fail(S12_ERR_UNSUPPORTED, "%s: n=%d must be a positive multiple of 4", who, n);
+    if (n > c->capacity) return fail(S12_ERR_TOO_LARGE, "%s: n=%d exceeds the communicator's capacity %d", who, n, c->capacity);
+    if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return fail(S12_ERR_UNSUPPORTED, "%s: buffers must be 16-byte aligned", who);
+    AllReduceParams P = {};
+    if (fill_rank(c, P.r[0])) return fail(S12_ERR_CUDA, "%s: no status word", who);
+    P.in[0] = (const float*)in; P.out[0] = (float*)out;
+    P.world = c->world; P.capacity = c->capacity; P.n = n;
+    return launch(allreduce_kernel, dim3(comm_ctas(n), 1), dim3(kCommThreads), 0, stream, who, P);
+}
+
+// Test hook for a single GPU: the `world` ranks of communicators connected with s12_comm_connect_local run as
+// ONE cooperative launch (blockIdx.y = rank), so that ranks waiting on one another are resident together.
+int s12_allreduce_f32_emulated_async(S12Comm* const* comms, int world, const void* const* ins, void* const* outs, int n,
+                                     void* stream)
+{
+    using namespace s12;
+    const char* who = "s12_allreduce_f32_emulated_async";
+    if (!comms || !ins || !outs || world < 1 || world > kCommMaxWorld) return fail(S12_ERR_BAD_ARG, "%s: bad argument", who);
+    if (n < 4 || (n & 3) || n > comms[0]->capacity) return fail(S12_ERR_UNSUPPORTED, "%s: n=%d", who, n);
+    AllReduceParams P = {};
+    for (int r = 0; r < world; r++) {
+        if (!comms[r] || !comms[r]->connected) return fail(S12_ERR_BAD_ARG, "%s: communicator %d not connected", who, r);
+        if (fill_rank(comms[r], P.r[r])) return fail(S12_ERR_CUDA, "%s: no status word", who);
+        P.in[r] = (const float*)ins[r]; P.out[r] = (float*)outs[r];
+    }
+    P.world = world; P.capacity = comms[0]->capacity; P.n = n;
+    const int ctas = comm_ctas(n);
+    int per_sm = 0;
+    int rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_kernel, kCommThreads, 0), who);
+    if (rc) return rc;
+    if ((long long)ctas * world > (long long)per_sm * sm_count())
+        return fail(S12_ERR_TOO_LARGE, "%s: %d x %d CTAs cannot be resident together", who, ctas, world);
+    void* args[1] = {&P};
+    return check_cuda(cudaLaunchCooperativeKernel((const void*)allreduce_kernel, dim3(ctas, world), dim3(kCommThreads), args, 0,
+                                                  (cudaStream_t)stream), who);
+}
+
+int s12_comm_destroy(S12Comm* c)
+{
+    if (!c) return S12_OK;
+    cudaDeviceSynchronize();
+    for (int p = 0; p < c->world; p++)
+        if (c->opened[p] && c->peer_base[p]) cudaIpcCloseMemHandle(c->peer_base[p]);
+    if (c->base) cudaFree(c->base);
+    if (c->seq) cudaFree(c->seq);
+    delete c;
+    return S12_OK;
+}
+
+}  // extern "C"

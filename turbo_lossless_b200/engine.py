@@ -314,3 +314,65 @@ class Split12Engine:
 
     def device_status(self) -> int:
         return int(self.lib.s12_device_status())
+
+
+class TPComm:
+    """All-reduce of fp32 partial results across tensor-parallel ranks (s12_comm_* of the C ABI).
+
+    One process per GPU: ``TPComm(rank, world, max_floats, group)`` allocates this rank's receive
+    area, exchanges the handles with an ``all_gather_object`` on the given ``torch.distributed``
+    group (the plumbing), and maps the peers' areas; ``all_reduce`` is then one kernel of this
+    library on the caller's stream.  ``TPComm.local(world, max_floats)`` builds ``world``
+    communicators inside one process on one device for tests.
+    """
+
+    def __init__(self, rank: int, world: int, max_floats: int, group=None, _connect: bool = True):
+        self.lib = capi.load()
+        self.rank, self.world, self.max_floats = rank, world, max_floats
+        self._h = C.c_void_p()
+        nbytes = int(self.lib.s12_comm_handle_bytes())
+        handle = C.create_string_buffer(nbytes)
+        check(self.lib.s12_comm_create(rank, world, max_floats, C.byref(self._h), handle), "s12_comm_create")
+        if _connect:
+            if world > 1:
+                import torch.distributed as dist
+                gathered = [None] * world
+                dist.all_gather_object(gathered, handle.raw, group=group)
+                blob = b"".join(gathered)
+            else:
+                blob = handle.raw
+            check(self.lib.s12_comm_connect(self._h, blob), "s12_comm_connect")
+
+    @classmethod
+    def local(cls, world: int, max_floats: int):
+        comms = [cls(r, world, max_floats, _connect=False) for r in range(world)]
+        arr = (C.c_void_p * world)(*[c._h for c in comms])
+        check(comms[0].lib.s12_comm_connect_local(arr, world), "s12_comm_connect_local")
+        return comms
+
+    def all_reduce(self, src: torch.Tensor, dst: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        dst = src if dst is None else dst
+        check(self.lib.s12_allreduce_f32_async(self._h, _ptr(src), _ptr(dst), src.numel(), _stream(stream)),
+              "s12_allreduce_f32_async")
+        return dst
+
+    @staticmethod
+    def all_reduce_emulated(comms, srcs, dsts, stream=None) -> None:
+        """All ranks of ``TPComm.local`` communicators in one cooperative launch (single-GPU tests)."""
+        world = len(comms)
+        arr = (C.c_void_p * world)(*[c._h for c in comms])
+        ins = (C.c_void_p * world)(*[s.data_ptr() for s in srcs])
+        outs = (C.c_void_p * world)(*[d.data_ptr() for d in dsts])
+        check(comms[0].lib.s12_allreduce_f32_emulated_async(arr, world, ins, outs, srcs[0].numel(), _stream(stream)),
+              "s12_allreduce_f32_emulated_async")
+
+    def close(self) -> None:
+        if self._h:
+            self.lib.s12_comm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
