@@ -59,9 +59,11 @@ def parse_args():
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (development only)")
-    ap.add_argument("--comm", default="own", choices=["own", "nccl"],
-                    help="all-reduce after the row-parallel projections at N > 1: this library's one-shot kernel over "
-                         "peer memory (inside the step's CUDA graph) or NCCL called between graph segments")
+    ap.add_argument("--comm", default="own", choices=["own", "fused", "nccl"],
+                    help="all-reduce after the row-parallel projections at N > 1: own = this library's one-shot kernel over "
+                         "peer memory as a node of the step's CUDA graph (fastest measured: the next GEMV prefetches its "
+                         "weights while it runs); fused = the B=1 GEMV pushes its rows to the peers and adds them itself "
+                         "(one kernel, but its CTAs stay resident while they wait); nccl = NCCL between graph segments")
     return ap.parse_args()
 
 
@@ -187,7 +189,8 @@ def run_ours(args):
     layers = args.layers or cfg["layers"]
     B, H, V = cfg["batch"], cfg["hidden"], cfg["vocab"]
     eng = Split12Engine()
-    comm = TPComm(rank, world, B * H) if (world > 1 and args.comm == "own") else None
+    comm = TPComm(rank, world, B * H) if (world > 1 and args.comm != "nccl") else None
+    use_fused = comm is not None and args.comm == "fused" and B == 1
     _log("process group up; building model")
     model = build_model(cfg, rank, world, layers, torch, CompressedWeight)
     _log("model packed")
@@ -237,6 +240,11 @@ def run_ours(args):
     # one small graph per segment and calls all_reduce between them.
     segments = []
 
+    def fused(w, x, out):
+        """Row-parallel GEMV and the sum over ranks as one kernel (B = 1)."""
+        comm.gemv_all_reduce(w, x, out)
+        launches[0] += 1
+
     def all_reduce(t):
         if comm is not None:
             def ar(t=t):
@@ -256,16 +264,22 @@ def run_ours(args):
     for L in model["layers"]:
         if "wk" in L:
             add_k(lambda L=L: proj([L["wq"], L["wk"], L["wv"]], x_hidden, [o_q, o_k, o_v]))
-            add_k(lambda L=L: proj([L["wo"]], x_attn, [o_o]))
-            if world > 1:
-                all_reduce(o_o)
+            if use_fused:
+                add_k(lambda L=L: fused(L["wo"], x_attn, o_o))
+            else:
+                add_k(lambda L=L: proj([L["wo"]], x_attn, [o_o]))
+                if world > 1:
+                    all_reduce(o_o)
         else:
             add_k(lambda L=L: proj([L["wq"]], x_hidden, [o_q]))
         if "w_gate" in L:
             add_k(lambda L=L: proj([L["w_gate"], L["w_up"]], x_hidden, [o_g, o_u]))
-            add_k(lambda L=L: proj([L["w_down"]], x_ffn, [o_d]))
-            if world > 1:
-                all_reduce(o_d)
+            if use_fused:
+                add_k(lambda L=L: fused(L["w_down"], x_ffn, o_d))
+            else:
+                add_k(lambda L=L: proj([L["w_down"]], x_ffn, [o_d]))
+                if world > 1:
+                    all_reduce(o_d)
     if model["lm_head"] is not None:
         add_k(lambda: proj([model["lm_head"]], x_hidden, [logits]))
 
@@ -333,8 +347,11 @@ def run_ours(args):
         _log(f"timed region done: {ms / args.steps:.3f} ms/step")
 
         # end to end: pinned host activations in, logits back to the host, every step
-        for _ in range(2):
+        for i in range(2):
             x_hidden.copy_(x_host, non_blocking=True); run(); logits_host.copy_(logits, non_blocking=True)
+            if os.environ.get("S12_BENCH_VERBOSE"):
+                stream.synchronize()
+                _log(f"end-to-end warm-up step {i} done, device status {eng.device_status():#x}")
         barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
@@ -386,7 +403,8 @@ def run_ours(args):
         "config": {"workload": args.workload, "what": cfg["desc"], "layers": layers, "batch": B,
                    "parallelism": f"tp{world}" if world > 1 else "single",
                    "collective": ("none" if world == 1 else
-                                  "one-shot all-reduce kernel over NVLink peer memory, inside the step's graph" if comm is not None
+                                  ("row-parallel GEMV fused with its one-shot all-reduce over NVLink peer memory (one kernel)" if use_fused
+                                   else "one-shot all-reduce kernel over NVLink peer memory, inside the step's graph") if comm is not None
                                   else "NCCL all_reduce between graph segments"),
                    "l2": "inputs larger than L2 (packed weights of one step: %.2f GB per GPU)" % (total_bytes / world / 1e9),
                    "launch": ("cuda graph" if graph is not None else "eager") + ("" if args.no_pdl else " + programmatic dependent launch"),

@@ -309,6 +309,14 @@ int s12_comm_connect(S12Comm* comm, const void* all_handles);
  * 16-byte aligned, may alias.  Every rank must issue the same sequence of
  * calls with the same n.  Asynchronous on `stream`; capturable. */
 int s12_allreduce_f32_async(S12Comm* comm, const void* in, void* out, int n, void* stream);
+/* Row-parallel GEMV and its all-reduce as ONE kernel (B = 1): out[m] = sum
+ * over ranks of (this rank's shard w) . act.  The streaming GEMV's epilogue
+ * writes every finished row straight into all ranks' receive areas while the
+ * rest of the tensor is still streaming, then each CTA adds the ranks' partials
+ * of its own rows.  Shards must have the same M and K on every rank; M a
+ * multiple of 4, <= max_floats.  Falls back to s12_gemv_async followed by
+ * s12_allreduce_f32_async when the streaming kernel does not take the shape. */
+int s12_gemv_allreduce_async(S12Comm* comm, const S12Tensor* w, const void* act, void* out, void* stream);
 int s12_comm_destroy(S12Comm* comm);
 /* Test support for a single GPU: `world` communicators created in one process
  * on one device are wired to each other, and one cooperative launch runs all

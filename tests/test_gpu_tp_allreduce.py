@@ -54,6 +54,29 @@ def test_rejects_bad_sizes():
     c.close()
 
 
+@pytest.mark.parametrize("M,K", [(4096, 4096), (4096, 2048), (1000, 512), (4100, 1024)])
+def test_fused_gemv_allreduce_world_of_one(M, K):
+    """s12_gemv_allreduce_async on one rank: the push / signal / wait / add path of the GEMV epilogue runs
+    against the rank's own receive area, and consecutive calls alternate the areas."""
+    import torch
+    from oracle import oracle as O
+    from turbo_lossless_b200 import CompressedWeight, Split12Engine, TPComm
+    eng = Split12Engine()
+    (comm,) = TPComm.local(1, 8192)
+    w = O.synth_weights(M, K, 5, outlier_frac=1e-3)
+    cw = CompressedWeight.from_packed(O.pack(w))
+    for call in range(3):
+        x = O.synth_acts(1, K, 40 + call)
+        xd = torch.from_numpy(x.view(np.int16)).cuda()
+        out = torch.full((M,), float("nan"), device="cuda")
+        comm.gemv_all_reduce(cw, xd, out)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        ref = O.gemm_exact(w, x)[0]
+        np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=0, atol=1e-4 * np.abs(ref).max())
+    comm.close()
+
+
 _WORKER = r"""
 import os, sys
 import numpy as np, torch, torch.distributed as dist
@@ -74,6 +97,25 @@ for call, n in enumerate([4096, 4096, 14336, 1 << 20, 4096]):
     for p in parts:
         ref = ref + p
     ok = ok and np.array_equal(out.cpu().numpy(), ref) and eng.device_status() == 0
+# row-parallel GEMV fused with its all-reduce: each rank holds a column slice of W
+from oracle import oracle as O
+from turbo_lossless_b200 import CompressedWeight
+for call, (M, K) in enumerate([(4096, 4096), (4096, 14336), (1000, 1024)]):
+    w = O.synth_weights(M, K, 77 + call, outlier_frac=1e-3)
+    x = O.synth_acts(1, K, 5 + call)
+    ks = K // world
+    wr = np.ascontiguousarray(w[:, rank * ks:(rank + 1) * ks])
+    cw = CompressedWeight.from_packed(O.pack(wr))
+    xd = torch.from_numpy(np.ascontiguousarray(x[:, rank * ks:(rank + 1) * ks]).view(np.int16)).cuda()
+    out = torch.full((M,), float("nan"), device="cuda")
+    comm.gemv_all_reduce(cw, xd, out)
+    torch.cuda.synchronize()
+    ref = O.gemm_exact(w, x)[0]
+    got = out.cpu().numpy()
+    ok = ok and bool(np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()) and eng.device_status() == 0
+    gathered = [None] * world
+    dist.all_gather_object(gathered, got.tobytes())
+    ok = ok and all(g == gathered[0] for g in gathered)      # bit-identical on every rank
 dist.barrier()
 comm.close()
 dist.destroy_process_group()

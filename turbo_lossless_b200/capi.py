@@ -64,6 +64,7 @@ SIGNATURES = {
     "s12_comm_connect_local": (_i, [C.POINTER(_vp), _i]),
     "s12_allreduce_f32_async": (_i, [_vp, _vp, _vp, _i, _vp]),
     "s12_allreduce_f32_emulated_async": (_i, [C.POINTER(_vp), _i, C.POINTER(_vp), C.POINTER(_vp), _i, _vp]),
+    "s12_gemv_allreduce_async": (_i, [_vp, C.POINTER(S12Tensor), _vp, _vp, _vp]),
     "s12_comm_destroy": (_i, [_vp]),
 }
 

@@ -15,48 +15,16 @@
 // store the call's token into every rank's flag for (this CTA, my rank); wait
 // (bounded) until the tokens of all source ranks have arrived here; add the
 // world partials in rank order (every rank gets bit-identical sums) and store.
-// Consecutive calls alternate between the two parities: a rank can be at most
-// one call ahead of a peer, because finishing call k needs the peer's data of
-// call k, so two areas are enough.  The call counter lives in device memory
-// (one per CTA), which makes the kernel replayable from a CUDA graph.
+// Consecutive calls alternate between the two parities (comm.cuh explains why
+// two areas are enough).  The call counter lives in device memory, which makes
+// the kernel replayable from a CUDA graph.
 //
 // Plain peer stores and loads only: no multimem, no TMA.
-#include "common.cuh"
+#include "comm.cuh"
 #include <mutex>
 #include <vector>
 
 namespace s12 {
-
-constexpr int kCommMaxWorld = 8;
-constexpr int kCommMaxCtas = 64;
-constexpr int kCommThreads = 512;
-constexpr int kCommMinSlice = 2048;          // floats per CTA before another CTA is added
-
-struct CommRank {
-    float* recv[kCommMaxWorld];              // every rank's receive area (index = owner rank), as mapped here
-    unsigned int* flags[kCommMaxWorld];      // every rank's flag area
-    unsigned int* seq;                       // [kMaxCtas] calls completed, local
-    unsigned int* status;                    // local status word (bit 0x8000: a wait gave up)
-    int rank;
-};
-
-struct AllReduceParams {
-    CommRank r[kCommMaxWorld];               // [0] in a real launch; [y] when several ranks are emulated in one launch
-    const float* in[kCommMaxWorld];
-    float* out[kCommMaxWorld];
-    int world, capacity, n;
-};
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v)
-{
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p)
-{
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 __global__ void __launch_bounds__(kCommThreads)
 allreduce_kernel(const __grid_constant__ AllReduceParams P)
@@ -65,21 +33,17 @@ allreduce_kernel(const __grid_constant__ AllReduceParams P)
     const float* in = P.in[blockIdx.y];
     float* out = P.out[blockIdx.y];
     const int world = P.world, me = R.rank, cta = blockIdx.x;
-    __shared__ unsigned int s_seq;
-    __shared__ int s_giveup;
-    grid_launch_dependents();
-    if (threadIdx.x == 0) { s_seq = R.seq[cta]; s_giveup = 0; }
-    __syncthreads();
-    const unsigned int token = s_seq + 1u;
-    const int parity = (int)(s_seq & 1u);
+    if (P.early_trigger) grid_launch_dependents();                // the next projection may prefetch its weights meanwhile
+    grid_dependency_wait();                                       // `in` and the call counter come from earlier kernels
+    int parity;
+    const unsigned int token = comm_begin(R, parity);
 
     // this CTA's slice, in float4 units
     const int n4 = P.n >> 2;
     const int lo = (int)((long long)n4 * cta / gridDim.x), hi = (int)((long long)n4 * (cta + 1) / gridDim.x);
     const size_t row = (size_t)P.capacity;
 
-    grid_dependency_wait();                                       // `in` comes from the preceding kernel
-    // 1. push my partial slice into every rank's receive row for me
+    // push my partial slice into every rank's receive row for me
     for (int i = lo + threadIdx.x; i < hi; i += kCommThreads) {
         const float4 v = reinterpret_cast<const float4*>(in)[i];
 #pragma unroll 1
@@ -88,20 +52,10 @@ allreduce_kernel(const __grid_constant__ AllReduceParams P)
     }
     __threadfence_system();
     __syncthreads();
-    // 2. tell every rank that my slice has arrived
-    if ((int)threadIdx.x < world)
-        st_release_sys(R.flags[threadIdx.x] + ((size_t)parity * kCommMaxCtas + cta) * world + me, token);
-    // 3. wait for every rank's slice (bounded: about two seconds)
-    if ((int)threadIdx.x < world) {
-        const unsigned int* f = R.flags[me] + ((size_t)parity * kCommMaxCtas + cta) * world + threadIdx.x;
-        unsigned int spins = 0;
-        while ((int)(ld_acquire_sys(f) - token) < 0) {
-            if (++spins > (1u << 23)) { atomicOr(R.status, 0x8000u); s_giveup = 1; break; }
-            __nanosleep(200);
-        }
-    }
+    comm_signal_and_wait(R, world, parity, cta, token, threadIdx.x);
     __syncthreads();
-    // 4. add the partials in rank order
+    if (!P.early_trigger) grid_launch_dependents();
+    // add the partials in rank order
     const float* mine = R.recv[me] + (size_t)parity * world * row;
     for (int i = lo + threadIdx.x; i < hi; i += kCommThreads) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -112,7 +66,8 @@ allreduce_kernel(const __grid_constant__ AllReduceParams P)
         }
         reinterpret_cast<float4*>(out)[i] = acc;
     }
-    if (threadIdx.x == 0) R.seq[cta] = token;
+    __syncthreads();
+    if (threadIdx.x == 0) comm_retire(R, token, gridDim.x);
 }
 
 }  // namespace s12
@@ -127,7 +82,7 @@ struct S12Comm {
     size_t recv_bytes = 0, flag_bytes = 0;
     char* peer_base[s12::kCommMaxWorld] = {};  // every rank's allocation as mapped in this process
     bool opened[s12::kCommMaxWorld] = {};      // mapped through an IPC handle (must be closed)
-    unsigned int* seq = nullptr;
+    unsigned int* calls = nullptr;             // [0] calls completed, [1] CTAs done in the running call
     bool connected = false;
 };
 
@@ -151,15 +106,15 @@ int s12_comm_create(int rank, int world, long long max_floats, S12Comm** out, vo
     c->flag_bytes = (size_t)2 * kCommMaxCtas * world * sizeof(unsigned int);
     if (!rc) rc = check_cuda(cudaMalloc(&c->base, c->recv_bytes + c->flag_bytes), who);
     if (!rc) rc = check_cuda(cudaMemset(c->base, 0, c->recv_bytes + c->flag_bytes), who);
-    if (!rc) rc = check_cuda(cudaMalloc(&c->seq, kCommMaxCtas * sizeof(unsigned int)), who);
-    if (!rc) rc = check_cuda(cudaMemset(c->seq, 0, kCommMaxCtas * sizeof(unsigned int)), who);
+    if (!rc) rc = check_cuda(cudaMalloc(&c->calls, 2 * sizeof(unsigned int)), who);
+    if (!rc) rc = check_cuda(cudaMemset(c->calls, 0, 2 * sizeof(unsigned int)), who);
     if (!rc && handle_out) {
         cudaIpcMemHandle_t h;
         rc = check_cuda(cudaIpcGetMemHandle(&h, c->base), who);
         if (!rc) memcpy(handle_out, &h, sizeof h);
     }
     if (!rc) rc = check_cuda(cudaDeviceSynchronize(), who);
-    if (rc) { if (c->base) cudaFree(c->base); if (c->seq) cudaFree(c->seq); delete c; return rc; }
+    if (rc) { if (c->base) cudaFree(c->base); if (c->calls) cudaFree(c->calls); delete c; return rc; }
     c->peer_base[rank] = c->base;
     *out = c;
     return S12_OK;
@@ -207,7 +162,7 @@ static int fill_rank(const S12Comm* c, s12::CommRank& R)
         R.recv[p] = reinterpret_cast<float*>(c->peer_base[p]);
         R.flags[p] = reinterpret_cast<unsigned int*>(c->peer_base[p] + c->recv_bytes);
     }
-    R.seq = c->seq;
+    R.calls = c->calls;
     R.status = s12::device_status_word();
     R.rank = c->rank;
     return R.status ? S12_OK : S12_ERR_CUDA;
@@ -216,7 +171,7 @@ static int fill_rank(const S12Comm* c, s12::CommRank& R)
 static int comm_ctas(int n)
 {
     int ctas = n / s12::kCommMinSlice;
-    return ctas < 1 ? 1 : (ctas > s12::kCommMaxCtas ? s12::kCommMaxCtas : ctas);
+    return ctas < 1 ? 1 : (ctas > 64 ? 64 : ctas);
 }
 
 // out[i] = sum over ranks of in[i], i < n; n a multiple of 4, n <= capacity; in/out 16-byte aligned device
@@ -235,6 +190,8 @@ int s12_allreduce_f32_async(S12Comm* c, const void* in, void* out, int n, void* 
     if (fill_rank(c, P.r[0])) return fail(S12_ERR_CUDA, "%s: no status word", who);
     P.in[0] = (const float*)in; P.out[0] = (float*)out;
     P.world = c->world; P.capacity = c->capacity; P.n = n;
+    const char* e = getenv("S12_COMM_EARLY");                     // tuning knob, default on
+    P.early_trigger = e ? atoi(e) : 1;
     return launch(allreduce_kernel, dim3(comm_ctas(n), 1), dim3(kCommThreads), 0, stream, who, P);
 }
 
@@ -272,9 +229,18 @@ int s12_comm_destroy(S12Comm* c)
     for (int p = 0; p < c->world; p++)
         if (c->opened[p] && c->peer_base[p]) cudaIpcCloseMemHandle(c->peer_base[p]);
     if (c->base) cudaFree(c->base);
-    if (c->seq) cudaFree(c->seq);
+    if (c->calls) cudaFree(c->calls);
     delete c;
     return S12_OK;
 }
 
 }  // extern "C"
+
+namespace s12 {
+bool comm_device_view(const S12Comm* c, CommRank& R, int& world, int& capacity)
+{
+    if (!c || !c->connected || fill_rank(c, R)) return false;
+    world = c->world; capacity = c->capacity;
+    return true;
+}
+}  // namespace s12

@@ -107,10 +107,16 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 
 
 // ---------------------------------------------------------------------------
-// mbarrier + bulk-copy (TMA) wrappers.  Every wait is bounded: after kWaitSpins
-// failed polls the waiter records a site code in the device status word and
-// carries on, so a lost signal degrades to wrong results plus a status the
-// host can read, never to a hung GPU.
+// mbarrier + bulk-copy (TMA) wrappers.  Every wait is bounded in wall-clock
+// time (kWaitLimitNs): when it runs out the waiter records a site code in the
+// device status word and carries on, so a lost signal degrades to wrong results
+// plus a status the host can read, never to a hung GPU.  The bound is in time,
+// not in polls, because a kernel that started early under programmatic
+// dependent launch legitimately waits for as long as its predecessor runs --
+// and with a tensor-parallel predecessor that includes waiting for other GPUs.
+// (A poll-count bound was tried first: the hardware returns from a failed
+// try_wait far sooner than the suspend hint, the polls ran out after a few
+// milliseconds, and the kernel then ran on with incomplete data.)
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void* p)
 {
@@ -135,7 +141,14 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 // One poll: the thread may be suspended by the hardware for up to kWaitHintNs
 // before the instruction returns false.
 constexpr uint32_t kWaitHintNs = 500000u;
-constexpr uint32_t kWaitSpins = 1u << 12;      // polls before giving up: about two seconds in total
+constexpr unsigned long long kWaitLimitNs = 8000000000ull;   // 8 s: above every bounded wait of a predecessor
+constexpr unsigned long long kPeerWaitLimitNs = 2000000000ull;   // 2 s: waits on another CTA's or GPU's flag
+__device__ __forceinline__ unsigned long long global_time_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -162,10 +175,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
                                           volatile int* cta_abort = nullptr)
 {
     if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
 #pragma unroll 1
-    for (uint32_t i = 1; i < kWaitSpins; i++) {
+    for (uint32_t i = 1;; i++) {
         if (cta_abort && *cta_abort) return false;
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 0u) {                                    // look at the clock now and then
+            const unsigned long long now = global_time_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
+        }
     }
     if (status) atomicOr(status, site);
     if (cta_abort) *cta_abort = 1;

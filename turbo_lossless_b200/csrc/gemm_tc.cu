@@ -373,9 +373,11 @@ __device__ __forceinline__ void drain_chunks(const GemmParams& P, const GemmTens
         if (lane == 0) {
             for (int ci = 1; ci <= ncontrib; ci++) {
                 const unsigned int* f = P.flags + blockIdx.x + ci;
-                unsigned int spins = 0;
+                unsigned long long t0 = 0;
                 while (ld_acquire_u32(f) < (unsigned)W) {
-                    if (*(volatile int*)s_abort || ++spins > (1u << 22)) {   // ~2 s: give up, flag the launch
+                    const unsigned long long now = global_time_ns();
+                    if (t0 == 0) t0 = now;
+                    if (*(volatile int*)s_abort || now - t0 > kPeerWaitLimitNs) {   // give up, flag the launch
                         atomicOr(P.status, 0x4000u);
                         *(volatile int*)s_abort = 1;
                         break;
@@ -743,6 +745,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     }
 
     if (cs > 1) cluster_reduce(P, smem, tmem_base, b_accfull, &s_abort);
+    if (*(volatile int*)&s_abort)                                 // a wait gave up: let copies still in flight land before the CTA goes
+        for (int i = 0; i < 256; i++) __nanosleep(1000);
 
     tc_fence_before();
     __syncthreads();

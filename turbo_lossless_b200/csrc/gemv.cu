@@ -369,7 +369,7 @@ gemv_generic_kernel(const __grid_constant__ GemvParams P, int mode)
 }
 
 int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* outs, int mode,
-                    void* stream, const char* who, int* rc_out);
+                    void* stream, const char* who, int* rc_out, const S12Comm* comm);
 
 static int env_int(const char* name, int dflt)
 {
@@ -403,6 +403,7 @@ struct GemvCall {
     const void* x[16]; void* o[16]; int B;
     const void* esc_row_base; const void* esc_vals;
     const char* who;
+    const S12Comm* comm;                // tensor-parallel call: the result is summed over the communicator's ranks
 };
 
 int gemv_dispatch(const GemvCall& c, void* stream)
@@ -477,9 +478,12 @@ int gemv_dispatch(const GemvCall& c, void* stream)
         int rc = S12_OK;
         void* outs[S12_MAX_MULTI];
         for (int i = 0; i < c.nt; i++) outs[i] = c.o[i];
-        int used = gemv_stream_try(c.w, c.nt, c.x[0], outs, mode, stream, who, &rc);
+        int used = gemv_stream_try(c.w, c.nt, c.x[0], outs, mode, stream, who, &rc, c.comm);
         if (used != 0) return rc;
-        return S12_GEMV_MODE(0);
+        rc = S12_GEMV_MODE(0);
+        // tensor-parallel call that the streaming kernel did not take: plain GEMV, then the all-reduce kernel
+        if (rc == S12_OK && c.comm) rc = s12_allreduce_f32_async(const_cast<S12Comm*>(c.comm), outs[0], outs[0], c.w[0].M, stream);
+        return rc;
     }
     if (c.B <= 8) return S12_GEMV_MODE(1);
     return S12_GEMV_MODE(2);
@@ -517,6 +521,17 @@ int s12_gemv_async(const S12Tensor* w, int num_tensors, const void* act, void* c
     c.w = w; c.nt = num_tensors; c.B = 1; c.who = "s12_gemv_async";
     c.x[0] = act;
     for (int i = 0; i < num_tensors; i++) c.o[i] = outs[i];
+    return gemv_dispatch(c, stream);
+}
+
+int s12_gemv_allreduce_async(S12Comm* comm, const S12Tensor* w, const void* act, void* out, void* stream)
+{
+    using namespace s12;
+    if (!comm || !w || !out) return fail(S12_ERR_BAD_ARG, "s12_gemv_allreduce_async: null argument");
+    if (w->M < 4 || (w->M & 3)) return fail(S12_ERR_UNSUPPORTED, "s12_gemv_allreduce_async: M=%d must be a positive multiple of 4", w->M);
+    GemvCall c = {};
+    c.w = w; c.nt = 1; c.B = 1; c.who = "s12_gemv_allreduce_async";
+    c.x[0] = act; c.o[0] = out; c.comm = comm;
     return gemv_dispatch(c, stream);
 }
 

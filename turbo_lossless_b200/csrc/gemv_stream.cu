@@ -37,7 +37,7 @@
 //     immediately (weights are never written); only the consumers' staging of
 //     the activation vector and the epilogue's stores wait for the predecessor.
 //   * All mbarrier waits are bounded (common.cuh).
-#include "common.cuh"
+#include "comm.cuh"
 #include <cstdlib>
 
 namespace s12 {
@@ -82,6 +82,11 @@ struct StreamParams {
     int total_blocks;
     unsigned int* status;
     DecodeMul mul;          // {128, 8, 1<<24}: see decode8_fma
+    // Tensor-parallel form (row-parallel shard, one tensor): the epilogue pushes every finished row to
+    // all ranks' receive areas instead of storing it, and the CTA then adds the ranks' partials of its
+    // own rows (protocol in comm.cuh).  tp_world == 0: plain store.
+    CommRank tp;
+    int tp_world, tp_cap;
 #ifdef S12_TRACE
     int trace_slot;
 #endif
@@ -147,7 +152,10 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
     }
     mbar_fence_init();
     __syncthreads();
-    grid_launch_dependents();
+    // The next kernel may start (and prefetch its weights) right away.  In the tensor-parallel form this
+    // CTA keeps its shared memory until the peers have arrived, so an early start would gain nothing:
+    // there the dependents are released after the wait.
+    if (P.tp_world == 0) grid_launch_dependents();
 
     // this CTA's contiguous range of row blocks
     const int b0 = (int)(((long long)blockIdx.x * P.total_blocks) / gridDim.x);
@@ -325,6 +333,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
     // the row's escapes.  The corrections are computed before waiting for the
     // consumers, so their global-memory latency overlaps the streaming.
     const int e = warp - kConsumers - 1;
+    const int tpw = P.tp_world;
+    int tp_parity = 0;
+    const unsigned int tp_token = tpw ? comm_begin(P.tp, tp_parity) : 0u;   // after grid_dependency_wait above
     const int gb = 16 / R;                                   // blocks per pass
     const int rho = lane & 15, sub = lane >> 4;
     const int ngroups = (nblocks + gb - 1) / gb;
@@ -356,11 +367,39 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             const int w1 = P.tpr == 1 ? w0 + kGroupWarps : kConsumers;
             for (int w = w0; w < w1; w++)
                 for (int q = 0; q < Q; q++) v += r[w * 16 + q * R + rho % R];
-            if (row < T.M) T.out[row] = v;
+            if (row < T.M) {
+                if (tpw == 0) {
+                    T.out[row] = v;
+                } else {
+                    const size_t at = ((size_t)tp_parity * tpw + P.tp.rank) * (size_t)P.tp_cap + row;
+                    for (int p = 0; p < tpw; p++) P.tp.recv[p][at] = v;
+                }
+            }
         }
         __syncwarp();
         if (lane == 0)
             for (int j = jfirst; j <= jlast; j++) mbar_arrive(bar_redfree + 8 * (j % kRedSlots));
+    }
+    if (tpw) {
+        // every row of this CTA is on its way to all ranks: signal, wait for the same CTA of every rank,
+        // add the partials of my rows in rank order
+        constexpr int kEpiThreads = kEpiWarps * 32;
+        const int tid = e * 32 + lane;
+        __threadfence_system();
+        named_bar_sync(5, kEpiThreads);
+        comm_signal_and_wait(P.tp, tpw, tp_parity, blockIdx.x, tp_token, tid);
+        named_bar_sync(5, kEpiThreads);
+        grid_launch_dependents();
+        const StreamTensor& T = P.t[0];
+        const int row_lo = b0 * R, row_hi = b1 * R < T.M ? b1 * R : T.M;
+        const float* mine = P.tp.recv[P.tp.rank] + (size_t)tp_parity * tpw * (size_t)P.tp_cap;
+        for (int row = row_lo + tid; row < row_hi; row += kEpiThreads) {
+            float acc = 0.f;
+            for (int p = 0; p < tpw; p++) acc += __ldcg(mine + (size_t)p * P.tp_cap + row);
+            T.out[row] = acc;
+        }
+        named_bar_sync(5, kEpiThreads);
+        if (tid == 0) comm_retire(P.tp, tp_token, gridDim.x);
     }
     if (e == 0) S12_STAMP(5);
 }
@@ -374,7 +413,7 @@ static int env_int2(const char* name, int dflt)
 // Returns 1 and launches when the streaming kernel applies; 0 when the caller
 // should use the register-pipelined kernel; negative on error.
 int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* outs, int mode,
-                    void* stream, const char* who, int* rc_out)
+                    void* stream, const char* who, int* rc_out, const S12Comm* comm)
 {
     const int impl = env_int2("S12_GEMV_IMPL", 1);              // 0: never, 1: auto (tuning/test knobs)
     const int force_r = env_int2("S12_GEMV_R", 0);
@@ -408,6 +447,11 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
         t.blk_end = blocks;
     }
     P.total_blocks = blocks;
+    if (comm) {
+        int world = 0, cap = 0;
+        if (nt != 1 || !comm_device_view(comm, P.tp, world, cap) || w[0].M > cap) return 0;
+        P.tp_world = world; P.tp_cap = cap;
+    }
     P.status = device_status_word();
     P.mul.m128 = 128u; P.mul.m8 = 8u; P.mul.hi24 = 1u << 24;
 #ifdef S12_TRACE
@@ -464,6 +508,7 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     }
     const int slots = sms * ctas;
     const int grid = blocks < slots ? blocks : slots;
+    if (comm && grid > kCommMaxCtas) return 0;
     *rc_out = launch(kern, dim3(grid), dim3(stream_threads(groups)), smem, stream, who, P);
     return *rc_out == S12_OK ? 1 : -1;
 }

@@ -356,6 +356,13 @@ class TPComm:
               "s12_allreduce_f32_async")
         return dst
 
+    def gemv_all_reduce(self, w: "CompressedWeight", bf16_in: torch.Tensor, out: torch.Tensor, stream=None,
+                        exact: bool = True) -> None:
+        """Row-parallel shard x activations and the sum over ranks as one kernel (B = 1)."""
+        t = w.tensor(with_csr=exact)
+        check(self.lib.s12_gemv_allreduce_async(self._h, C.byref(t), _ptr(bf16_in), _ptr(out), _stream(stream)),
+              "s12_gemv_allreduce_async")
+
     @staticmethod
     def all_reduce_emulated(comms, srcs, dsts, stream=None) -> None:
         """All ranks of ``TPComm.local`` communicators in one cooperative launch (single-GPU tests)."""
