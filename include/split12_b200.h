@@ -283,6 +283,59 @@ int s12_pack_fill_async(const void* bf16, int M, int K, int base_exp, const void
                         void* cols, void* correct, void* wrong, void* stream);
 
 /* --------------------------------------------------------------------------
+ * The decode step around the projections (engine/kernels.hip)
+ * --------------------------------------------------------------------------
+ * Same names, argument order and buffer layouts as the engine's launchers, so
+ * engine/inference.cpp links unchanged; they return 0 / S12_ERR_* where the
+ * engine's return void.  `stream` is the engine's hipStream_t / cudaStream_t.
+ * bf16 is raw int16.  KV cache: int8 [max_seq][n_head_kv][head_dim] with one
+ * fp32 scale per (position, kv head); scale = absmax / 127.
+ *   launch_embed_lookup               engine/kernels.hip:142
+ *   launch_argmax, launch_argmax_batch                 :149, :154
+ *   launch_rope_store_kv (B = 1)                       :308
+ *   launch_rms_norm_bf16_batch, launch_add_rms_norm_bf16_batch,
+ *   launch_silu_mul_bf16_batch, launch_add_batch       :463-493
+ *   launch_attention_all_heads, ..._batch              :589, :695
+ *   launch_rope_batch, launch_store_kv_batch           :848, :860
+ * Not provided: launch_flash_attention[_batch] (:1107, :1120; the engine takes
+ * that route only from position 1024 on; launch_attention_all_heads here has
+ * no such length limit below ~50k positions). */
+int launch_embed_lookup(const int16_t* embd_table, const int* token_ids, float* output, int n_embd,
+                        int batch_size, int n_vocab, void* stream);
+int launch_argmax(const float* logits, int* result, int n, void* stream);
+int launch_argmax_batch(const float* logits, int* results, int n_vocab, int batch_size, void* stream);
+int launch_rms_norm_bf16_batch(const float* x, const float* weight, int16_t* y, int n, float eps,
+                               int batch_size, void* stream);
+int launch_add_rms_norm_bf16_batch(float* x, const float* residual, const float* weight, int16_t* y,
+                                   int n, float eps, int batch_size, void* stream);
+int launch_silu_mul_bf16_batch(const float* gate, const float* up, int16_t* out, int n, int batch_size,
+                               void* stream);
+int launch_add_batch(float* y, const float* x, int n, int batch_size, void* stream);
+int launch_rope_store_kv(float* q, float* k, const float* v, int8_t* kv_k, int8_t* kv_v,
+                         float* kv_scale_k, float* kv_scale_v, int head_dim, int n_head, int n_head_kv,
+                         int position, int max_seq, float theta, void* stream);
+int launch_rope_batch(float* q, float* k, const int* positions, int head_dim, int n_head, int n_head_kv,
+                      int q_stride, int k_stride, float theta, int batch_size, void* stream);
+int launch_store_kv_batch(const float* k, const float* v, int8_t* kv_k, int8_t* kv_v, float* kv_scale_k,
+                          float* kv_scale_v, const int* positions, int kv_dim, int max_seq, int n_head_kv,
+                          int head_dim, int batch_size, void* stream);
+int launch_attention_all_heads(const float* q, const int8_t* k_cache, const int8_t* v_cache,
+                               const float* kv_scale_k, const float* kv_scale_v, int16_t* output,
+                               int n_head, int n_head_kv, int head_dim, int seq_len, int max_seq,
+                               float scale, void* stream);
+int launch_attention_all_heads_batch(const float* q, const int8_t* kv_k, const int8_t* kv_v,
+                                     const float* kv_scale_k, const float* kv_scale_v, int16_t* output,
+                                     const int* positions, int n_head, int n_head_kv, int head_dim,
+                                     int max_seq, float scale, int batch_size, int kv_stride, void* stream);
+/* launch_store_kv_batch with a cache per sequence: sequence s writes at
+ * kv_k + s * kv_stride (int8 elements; scales at s * kv_stride / head_dim), the
+ * layout launch_attention_all_heads_batch reads.  The engine's own batched
+ * store has no such offset (engine/kernels.hip:784-788). */
+int s12_store_kv_batch(const float* k, const float* v, int8_t* kv_k, int8_t* kv_v, float* kv_scale_k,
+                       float* kv_scale_v, const int* positions, int n_head_kv, int head_dim,
+                       long long kv_stride, int batch_size, void* stream);
+
+/* --------------------------------------------------------------------------
  * Tensor parallelism: all-reduce after the row-parallel projections
  * --------------------------------------------------------------------------
  * No counterpart in the reference, which runs on one GPU.  When o / down are

@@ -8,7 +8,10 @@ import sys
 _PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_PATH = os.path.join(_PKG, "libsplit12_b200.so")
-SOURCES = ["runtime.cu", "decompress.cu", "patches.cu", "gemv.cu", "gemv_stream.cu", "gemm.cu", "gemm_tc.cu", "pack.cu", "comm.cu", "host.cpp"]
+SOURCES = ["runtime.cu", "decompress.cu", "patches.cu", "gemv.cu", "gemv_stream.cu", "gemm.cu", "gemm_tc.cu", "pack.cu", "comm.cu", "step.cu", "host.cpp"]
+# sources compiled without --use_fast_math: the decode-step kernels use sincosf / expf / division on values
+# where the fast intrinsics lose digits (RoPE angles of hundreds of radians)
+ACCURATE_MATH = {"step.cu"}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--use_fast_math"]
 
@@ -34,7 +37,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         obj = os.path.join(objdir, src.rsplit(".", 1)[0] + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        flags = [f for f in NVCC_FLAGS if not (src in ACCURATE_MATH and f == "--use_fast_math")]
+        cmd = [nvcc, *flags, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

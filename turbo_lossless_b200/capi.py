@@ -58,6 +58,19 @@ SIGNATURES = {
     "s12_pack_find_base_exp_host": (_i, [_vp]),
     "s12_pack_async": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "s12_pack_fill_async": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "launch_embed_lookup": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "launch_argmax": (_i, [_vp, _vp, _i, _vp]),
+    "launch_argmax_batch": (_i, [_vp, _vp, _i, _i, _vp]),
+    "launch_rms_norm_bf16_batch": (_i, [_vp, _vp, _vp, _i, C.c_float, _i, _vp]),
+    "launch_add_rms_norm_bf16_batch": (_i, [_vp, _vp, _vp, _vp, _i, C.c_float, _i, _vp]),
+    "launch_silu_mul_bf16_batch": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "launch_add_batch": (_i, [_vp, _vp, _i, _i, _vp]),
+    "launch_rope_store_kv": (_i, [_vp] * 7 + [_i, _i, _i, _i, _i, C.c_float, _vp]),
+    "launch_rope_batch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, C.c_float, _i, _vp]),
+    "launch_store_kv_batch": (_i, [_vp] * 7 + [_i, _i, _i, _i, _i, _vp]),
+    "launch_attention_all_heads": (_i, [_vp] * 6 + [_i, _i, _i, _i, _i, C.c_float, _vp]),
+    "launch_attention_all_heads_batch": (_i, [_vp] * 7 + [_i, _i, _i, _i, C.c_float, _i, _i, _vp]),
+    "s12_store_kv_batch": (_i, [_vp] * 7 + [_i, _i, C.c_longlong, _i, _vp]),
     "s12_comm_handle_bytes": (_i, []),
     "s12_comm_create": (_i, [_i, _i, C.c_longlong, C.POINTER(_vp), _vp]),
     "s12_comm_connect": (_i, [_vp, _vp]),

@@ -1,0 +1,530 @@
+// The small kernels either side of the split12 projections in a decode step:
+// embedding lookup, RMSNorm (with the residual add) to bf16, RoPE + INT8
+// per-head KV store, decode attention over the INT8 cache (GQA), SiLU(gate)*up
+// to bf16, residual add, greedy argmax.  Same entry-point names, argument order
+// and layouts as the engine's own launchers (engine/kernels.hip:127-160,
+// 306-336, 461-493, 588-603, 694-714, 847-880), so the engine's forward loop
+// (engine/inference.cpp:198-366, 572-666) links against this library unchanged.
+// The launchers return int (0 = ok) where the engine's return void; a caller
+// that ignores the value is unaffected.
+//
+// Written for this part rather than translated: every kernel takes part in
+// programmatic dependent launch (so the chain GEMV -> norm -> GEMV replays
+// from one CUDA graph without full kernel boundaries), loads are 16-byte
+// vectors where the layout allows, and the B=1 RoPE + KV store is one launch
+// instead of two.  Floating-point results agree with the engine's kernels to
+// rounding (different reduction trees, accurate sincosf instead of the fast
+// intrinsic); tests/test_gpu_step.py states the tolerances.
+#include "common.cuh"
+#include <cmath>
+#include <mutex>
+
+namespace s12 {
+
+__device__ __forceinline__ float bf16_raw_to_float(int16_t raw)
+{
+    return __uint_as_float(((uint32_t)(uint16_t)raw) << 16);
+}
+// round to nearest even, as engine/kernels.hip:22-28
+__device__ __forceinline__ int16_t float_to_bf16_rne(float v)
+{
+    const uint32_t u = __float_as_uint(v);
+    return (int16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+
+// block-wide sum / max over up to 32 warps; every thread gets the result
+template <bool kMax>
+__device__ __forceinline__ float block_reduce(float v, float* scratch /* >= 33 floats */)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float o = __shfl_xor_sync(0xFFFFFFFFu, v, off);
+        v = kMax ? fmaxf(v, o) : v + o;
+    }
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float w = lane < nwarps ? scratch[lane] : (kMax ? -INFINITY : 0.f);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float o = __shfl_xor_sync(0xFFFFFFFFu, w, off);
+            w = kMax ? fmaxf(w, o) : w + o;
+        }
+        if (lane == 0) scratch[32] = w;
+    }
+    __syncthreads();
+    const float r = scratch[32];
+    __syncthreads();                                              // scratch may be reused right away
+    return r;
+}
+
+// ---------------------------------------------------------------------------
+// embedding lookup (engine/kernels.hip:57-73): bf16 table row -> fp32; a token
+// outside [0, n_vocab) gives a zero row
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+embed_kernel(const int16_t* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ out,
+             int n_embd, int batch, int n_vocab)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int seq = blockIdx.y, idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (seq >= batch || idx >= n_embd) return;
+    const int tok = tokens[seq];
+    out[(size_t)seq * n_embd + idx] =
+        (tok < 0 || tok >= n_vocab) ? 0.f : bf16_raw_to_float(table[(size_t)tok * n_embd + idx]);
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm -> bf16, optionally after x += residual written back in place
+// (engine/kernels.hip:355-393, 399-442).  One CTA per sequence.
+// ---------------------------------------------------------------------------
+template <bool kAdd>
+__global__ void __launch_bounds__(1024)
+rms_norm_kernel(float* __restrict__ x, const float* __restrict__ residual, const float* __restrict__ weight,
+                int16_t* __restrict__ y, int n, float eps)
+{
+    __shared__ float scratch[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t off = (size_t)blockIdx.x * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[off + i];
+        if (kAdd) { v += residual[off + i]; x[off + i] = v; }
+        ss += v * v;
+    }
+    ss = block_reduce<false>(ss, scratch);
+    const float rms = rsqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        y[off + i] = float_to_bf16_rne(x[off + i] * rms * weight[i]);    // a thread re-reads only what it wrote
+}
+
+// SiLU(gate) * up -> bf16 (engine/kernels.hip:447-458), residual add (engine/kernels.hip:340-349)
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, int16_t* __restrict__ out, long long total)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float g = gate[i];
+    out[i] = float_to_bf16_rne(g / (1.0f + expf(-g)) * up[i]);
+}
+__global__ void __launch_bounds__(256)
+add_kernel(float* __restrict__ y, const float* __restrict__ x, long long total)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) y[i] += x[i];
+}
+
+// ---------------------------------------------------------------------------
+// RoPE on q and k (rotate-half form, engine/kernels.hip:174-215, 717-756) and
+// INT8 KV store with one scale per (position, kv head): scale = absmax/127,
+// value = clamp(rint(v * 127/absmax), -127, 127) (engine/kernels.hip:220-303,
+// 760-845).  One launch: CTA (h, seq) with h < n_head rotates q head h;
+// n_head <= h < n_head + n_head_kv rotates k head (written back, as the engine
+// does) and stores it; the last n_head_kv CTAs store v.  store == 0: rotation
+// only (launch_rope_batch); rope == 0: store only (launch_store_kv_batch).
+// ---------------------------------------------------------------------------
+struct RopeFreqs { float f[128]; };                              // head_dim <= 256
+
+struct RopeKvParams {
+    float* q; float* k; const float* v;
+    int8_t* kv_k; int8_t* kv_v; float* sc_k; float* sc_v;
+    const int* positions;       // null: every sequence uses `position`
+    int position;
+    int head_dim, n_head, n_head_kv;
+    int q_stride, k_stride;     // floats between sequences in q and k/v
+    long long kv_stride;        // int8 elements between the sequences' caches (0: one shared cache)
+    int rope, store;
+};
+
+__global__ void __launch_bounds__(256)
+rope_kv_kernel(const __grid_constant__ RopeKvParams P, const __grid_constant__ RopeFreqs F)
+{
+    __shared__ float scratch[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    const int hd = P.head_dim, half = hd >> 1;
+    const int pos = P.positions ? P.positions[seq] : P.position;
+    if (h < P.n_head) {
+        if (P.rope && d < half) {
+            float* p = P.q + (size_t)seq * P.q_stride + (size_t)h * hd;
+            float s, c;
+            sincosf((float)pos * F.f[d], &s, &c);
+            const float x0 = p[d], x1 = p[d + half];
+            p[d] = x0 * c - x1 * s;
+            p[d + half] = x0 * s + x1 * c;
+        }
+        return;
+    }
+    const bool is_v = h >= P.n_head + P.n_head_kv;
+    const int kvh = h - P.n_head - (is_v ? P.n_head_kv : 0);
+    float val = 0.f;
+    if (!is_v) {
+        float* p = P.k + (size_t)seq * P.k_stride + (size_t)kvh * hd;
+        if (P.rope) {
+            float lo = 0.f, hi = 0.f;
+            if (d < half) {
+                float s, c;
+                sincosf((float)pos * F.f[d], &s, &c);
+                const float x0 = p[d], x1 = p[d + half];
+                lo = x0 * c - x1 * s; hi = x0 * s + x1 * c;
+                p[d] = lo; p[d + half] = hi;
+            }
+            // thread d needs element d: the upper half comes from thread d - half
+            __shared__ float rot[256];
+            if (d < half) { rot[d] = lo; rot[d + half] = hi; }
+            __syncthreads();
+            if (d < hd) val = rot[d];
+        } else if (d < hd) {
+            val = p[d];
+        }
+    } else if (d < hd) {
+        val = P.v[(size_t)seq * P.k_stride + (size_t)kvh * hd + d];
+    }
+    if (!P.store) return;
+    const float amax = block_reduce<true>(d < hd ? fabsf(val) : 0.f, scratch);
+    const float inv = amax > 0.f ? 127.0f / amax : 0.f;
+    const size_t kv_dim = (size_t)P.n_head_kv * hd;
+    int8_t* dst = (is_v ? P.kv_v : P.kv_k) + (size_t)seq * P.kv_stride + (size_t)pos * kv_dim + (size_t)kvh * hd;
+    float* sc = (is_v ? P.sc_v : P.sc_k) + (size_t)seq * (P.kv_stride / hd) + (size_t)pos * P.n_head_kv + kvh;
+    if (d < hd) dst[d] = (int8_t)(int)fminf(fmaxf(rintf(val * inv), -127.f), 127.f);
+    if (d == 0) *sc = amax / 127.0f;
+}
+
+// ---------------------------------------------------------------------------
+// Decode attention over the INT8 cache (engine/kernels.hip:499-586, 606-692):
+// scores[t] = scale * sum_d q[d] * (k[t][d] * sk[t]); softmax over t <= pos;
+// out[d] = sum_t p[t] * (v[t][d] * sv[t]) -> bf16.  CTA = (q head, sequence),
+// 8 warps.  Scores: one warp per position, a lane holds four q values and
+// reads four int8 of the key row (128 contiguous bytes per warp).  Values:
+// thread (g, d) sums over its share of the positions, 128 contiguous bytes per
+// warp and position; the shares are added through shared memory.
+// ---------------------------------------------------------------------------
+struct AttnParams {
+    const float* q; const int8_t* kc; const int8_t* vc; const float* sk; const float* sv;
+    int16_t* out;
+    const int* positions;       // null: seq_len for every sequence
+    int seq_len;
+    int n_head, n_head_kv, head_dim;
+    long long kv_stride;
+    float scale;
+};
+
+constexpr int kAttnThreads = 256;
+
+__global__ void __launch_bounds__(kAttnThreads)
+attention_kernel(const __grid_constant__ AttnParams P)
+{
+    extern __shared__ float att_smem[];                           // scores[seq_len], then acc[groups][head_dim]
+    __shared__ float scratch[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const int hd = P.head_dim, kvh = head / (P.n_head / P.n_head_kv);
+    const int T = P.positions ? P.positions[seq] + 1 : P.seq_len;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = kAttnThreads / 32;
+    const size_t kv_dim = (size_t)P.n_head_kv * hd;
+    const int8_t* kc = P.kc + (size_t)seq * P.kv_stride + (size_t)kvh * hd;
+    const int8_t* vc = P.vc + (size_t)seq * P.kv_stride + (size_t)kvh * hd;
+    const float* sk = P.sk + (size_t)seq * (P.kv_stride / hd) + kvh;
+    const float* sv = P.sv + (size_t)seq * (P.kv_stride / hd) + kvh;
+    const float* q = P.q + ((size_t)seq * P.n_head + head) * hd;
+    float* scores = att_smem;
+    float* accs = att_smem + ((T + 3) & ~3);
+    const float scale = P.scale;
+
+    // scores: lane owns elements [4*lane + 128*j, +4) of the head
+    const int chunks = (hd + 127) / 128;
+    float qv[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int d = j * 128 + lane * 4 + e;
+            qv[j][e] = (j < chunks && d < hd) ? q[d] : 0.f;
+        }
+    for (int t = warp; t < T; t += nwarps) {
+        const int8_t* row = kc + (size_t)t * kv_dim;
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            if (j >= chunks) break;
+            const int d0 = j * 128 + lane * 4;
+            if (d0 + 3 < hd) {
+                const int w = *reinterpret_cast<const int*>(row + d0);       // rows start on multiples of head_dim (>= 4)
+                dot += qv[j][0] * (float)(int8_t)(w & 0xFF) + qv[j][1] * (float)(int8_t)((w >> 8) & 0xFF) +
+                       qv[j][2] * (float)(int8_t)((w >> 16) & 0xFF) + qv[j][3] * (float)(int8_t)(w >> 24);
+            } else {
+                for (int e = 0; e < 4; e++)
+                    if (d0 + e < hd) dot += qv[j][e] * (float)row[d0 + e];
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, off);
+        if (lane == 0) scores[t] = dot * sk[(size_t)t * P.n_head_kv] * scale;
+    }
+    __syncthreads();
+    float m = -1e30f;
+    for (int t = threadIdx.x; t < T; t += kAttnThreads) m = fmaxf(m, scores[t]);
+    m = block_reduce<true>(m, scratch);
+    float sum = 0.f;
+    for (int t = threadIdx.x; t < T; t += kAttnThreads) {
+        const float e = expf(scores[t] - m);
+        scores[t] = e * sv[(size_t)t * P.n_head_kv];              // fold the value scale into the weight
+        sum += e;
+    }
+    sum = block_reduce<false>(sum, scratch);
+    const float inv = 1.0f / sum;
+
+    // values: group g of threads takes positions g, g + groups, ...
+    const int groups = kAttnThreads / hd > 0 ? kAttnThreads / hd : 1;
+    const int g = threadIdx.x / hd, d = threadIdx.x % hd;
+    if (hd <= kAttnThreads) {
+        float acc = 0.f;
+        if (g < groups)
+            for (int t = g; t < T; t += groups) acc += scores[t] * (float)vc[(size_t)t * kv_dim + d];
+        if (g < groups) accs[g * hd + d] = acc;
+        __syncthreads();
+        if (threadIdx.x < hd) {
+            float a = 0.f;
+            for (int gg = 0; gg < groups; gg++) a += accs[gg * hd + threadIdx.x];
+            P.out[((size_t)seq * P.n_head + head) * hd + threadIdx.x] = float_to_bf16_rne(a * inv);
+        }
+    } else {
+        for (int dd = threadIdx.x; dd < hd; dd += kAttnThreads) {
+            float acc = 0.f;
+            for (int t = 0; t < T; t++) acc += scores[t] * (float)vc[(size_t)t * kv_dim + dd];
+            P.out[((size_t)seq * P.n_head + head) * hd + dd] = float_to_bf16_rne(acc * inv);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Greedy argmax, one CTA per sequence.  Ties resolve as in the engine's kernel
+// (engine/kernels.hip:90-122: 256 threads scan i = tid, tid + 256, ... with a
+// strict ">", then a halving tree in which slot t meets slot t + s and keeps its
+// own value on equality).  After the level with stride s, slot t holds the
+// winner among the threads congruent to t modulo s, so the last comparison is
+// even against odd threads, the one before 0 against 2 modulo 4, ...: among the
+// maxima the thread whose 8-bit index read backwards is smallest wins, and
+// inside a thread the smallest i.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ bool argmax_better(float v, int i, float bv, int bi)
+{
+    if (v > bv) return true;
+    if (v < bv || !(v == bv)) return false;
+    const unsigned r = __brev((unsigned)i & 255u), br = __brev((unsigned)bi & 255u);
+    return r < br || (r == br && i < bi);
+}
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ result, int n)
+{
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const float* row = logits + (size_t)blockIdx.x * n;
+    float bv = -INFINITY;
+    int bi = 0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = row[i];
+        if (argmax_better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+        const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
+        if (argmax_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        bv = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7FFFFFFF;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
+            if (argmax_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) result[blockIdx.x] = bi == 0x7FFFFFFF ? 0 : bi;
+    }
+}
+
+// frequencies as the engine computes them on the host (engine/kernels.hip:129-140)
+static void rope_freqs(int head_dim, float theta, RopeFreqs& F)
+{
+    static std::mutex mu;
+    static RopeFreqs cached;
+    static int c_dim = 0;
+    static float c_theta = 0.f;
+    std::lock_guard<std::mutex> lk(mu);
+    if (c_dim != head_dim || c_theta != theta) {
+        for (int d = 0; d < head_dim / 2 && d < 128; d++) cached.f[d] = 1.0f / powf(theta, (float)(2 * d) / (float)head_dim);
+        c_dim = head_dim; c_theta = theta;
+    }
+    F = cached;
+}
+
+static int rope_kv_launch(RopeKvParams& P, float theta, int batch, void* stream, const char* who)
+{
+    if (P.head_dim < 2 || P.head_dim > 256 || (P.head_dim & 1) || P.n_head < 0 || P.n_head_kv < 1 || batch < 1)
+        return fail(S12_ERR_UNSUPPORTED, "%s: head_dim must be even and <= 256, n_head_kv >= 1, batch >= 1", who);
+    RopeFreqs F;
+    rope_freqs(P.head_dim, theta, F);
+    const int threads = ((P.head_dim + 31) / 32) * 32;
+    const int heads = (P.rope ? P.n_head : 0);
+    // CTAs that would have nothing to do are not launched: q heads only when rotating, v heads only when storing
+    RopeKvParams Q = P;
+    if (!P.rope) { Q.n_head = 0; }
+    const int ctas = Q.n_head + P.n_head_kv + (P.store ? P.n_head_kv : 0);
+    (void)heads;
+    return launch(rope_kv_kernel, dim3(ctas, batch), dim3(threads), 0, stream, who, Q, F);
+}
+
+static int attention_launch(AttnParams& P, int max_len, int batch, void* stream, const char* who)
+{
+    if (P.head_dim < 4 || P.head_dim > 256 || (P.head_dim & 3) || P.n_head_kv < 1 || P.n_head < P.n_head_kv ||
+        P.n_head % P.n_head_kv != 0 || max_len < 1 || batch < 1)
+        return fail(S12_ERR_UNSUPPORTED, "%s: needs head_dim %% 4 == 0 and <= 256, n_head a multiple of n_head_kv, seq_len >= 1", who);
+    const int groups = kAttnThreads / P.head_dim > 0 ? kAttnThreads / P.head_dim : 1;
+    const size_t smem = ((size_t)((max_len + 3) & ~3) + (size_t)groups * P.head_dim) * sizeof(float);
+    if (smem > 200 * 1024) return fail(S12_ERR_TOO_LARGE, "%s: seq_len %d needs more shared memory than one CTA has", who, max_len);
+    static bool attr_set[64];
+    if (smem > 48 * 1024) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        dev = (dev < 0 || dev >= 64) ? 0 : dev;
+        if (!attr_set[dev]) {
+            int rc = check_cuda(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), who);
+            if (rc) return rc;
+            attr_set[dev] = true;
+        }
+    }
+    return launch(attention_kernel, dim3(P.n_head, batch), dim3(kAttnThreads), smem, stream, who, P);
+}
+
+}  // namespace s12
+
+using namespace s12;
+
+extern "C" {
+
+int launch_embed_lookup(const int16_t* embd_table, const int* token_ids, float* output, int n_embd, int batch_size,
+                        int n_vocab, void* stream)
+{
+    if (!embd_table || !token_ids || !output || n_embd < 1 || batch_size < 1) return fail(S12_ERR_BAD_ARG, "launch_embed_lookup: bad argument");
+    return launch(embed_kernel, dim3((n_embd + 255) / 256, batch_size), dim3(256), 0, stream, "launch_embed_lookup",
+                  embd_table, token_ids, output, n_embd, batch_size, n_vocab);
+}
+
+int launch_argmax_batch(const float* logits, int* results, int n_vocab, int batch_size, void* stream)
+{
+    if (!logits || !results || n_vocab < 1 || batch_size < 1) return fail(S12_ERR_BAD_ARG, "launch_argmax: bad argument");
+    return launch(argmax_kernel, dim3(batch_size), dim3(1024), 0, stream, "launch_argmax", logits, results, n_vocab);
+}
+int launch_argmax(const float* logits, int* result, int n, void* stream) { return launch_argmax_batch(logits, result, n, 1, stream); }
+
+int launch_rms_norm_bf16_batch(const float* x, const float* weight, int16_t* y, int n, float eps, int batch_size, void* stream)
+{
+    if (!x || !weight || !y || n < 1 || batch_size < 1) return fail(S12_ERR_BAD_ARG, "launch_rms_norm_bf16_batch: bad argument");
+    const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
+    return launch(rms_norm_kernel<false>, dim3(batch_size), dim3(threads), 0, stream, "launch_rms_norm_bf16_batch",
+                  const_cast<float*>(x), (const float*)nullptr, weight, y, n, eps);
+}
+int launch_add_rms_norm_bf16_batch(float* x, const float* residual, const float* weight, int16_t* y, int n, float eps,
+                                   int batch_size, void* stream)
+{
+    if (!x || !residual || !weight || !y || n < 1 || batch_size < 1) return fail(S12_ERR_BAD_ARG, "launch_add_rms_norm_bf16_batch: bad argument");
+    const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
+    return launch(rms_norm_kernel<true>, dim3(batch_size), dim3(threads), 0, stream, "launch_add_rms_norm_bf16_batch",
+                  x, residual, weight, y, n, eps);
+}
+int launch_silu_mul_bf16_batch(const float* gate, const float* up, int16_t* out, int n, int batch_size, void* stream)
+{
+    if (!gate || !up || !out || n < 1 || batch_size < 1) return fail(S12_ERR_BAD_ARG, "launch_silu_mul_bf16_batch: bad argument");
+    const long long total = (long long)n * batch_size;
+    return launch(silu_mul_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, "launch_silu_mul_bf16_batch",
+                  gate, up, out, total);
+}
+int launch_add_batch(float* y, const float* x, int n, int batch_size, void* stream)
+{
+    if (!y || !x || n < 1 || batch_size < 1) return fail(S12_ERR_BAD_ARG, "launch_add_batch: bad argument");
+    const long long total = (long long)n * batch_size;
+    return launch(add_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, "launch_add_batch", y, x, total);
+}
+
+int launch_rope_store_kv(float* q, float* k, const float* v, int8_t* kv_k, int8_t* kv_v, float* kv_scale_k, float* kv_scale_v,
+                         int head_dim, int n_head, int n_head_kv, int position, int max_seq, float theta, void* stream)
+{
+    if (!q || !k || !v || !kv_k || !kv_v || !kv_scale_k || !kv_scale_v) return fail(S12_ERR_BAD_ARG, "launch_rope_store_kv: null argument");
+    if (position < 0 || position >= max_seq) return fail(S12_ERR_BAD_ARG, "launch_rope_store_kv: position %d outside the cache of %d", position, max_seq);
+    RopeKvParams P = {};
+    P.q = q; P.k = k; P.v = v; P.kv_k = kv_k; P.kv_v = kv_v; P.sc_k = kv_scale_k; P.sc_v = kv_scale_v;
+    P.position = position; P.head_dim = head_dim; P.n_head = n_head; P.n_head_kv = n_head_kv;
+    P.q_stride = n_head * head_dim; P.k_stride = n_head_kv * head_dim; P.rope = 1; P.store = 1;
+    return rope_kv_launch(P, theta, 1, stream, "launch_rope_store_kv");
+}
+int launch_rope_batch(float* q, float* k, const int* positions, int head_dim, int n_head, int n_head_kv, int q_stride,
+                      int k_stride, float theta, int batch_size, void* stream)
+{
+    if (!q || !k || !positions) return fail(S12_ERR_BAD_ARG, "launch_rope_batch: null argument");
+    RopeKvParams P = {};
+    P.q = q; P.k = k; P.positions = positions; P.head_dim = head_dim; P.n_head = n_head; P.n_head_kv = n_head_kv;
+    P.q_stride = q_stride; P.k_stride = k_stride; P.rope = 1; P.store = 0;
+    return rope_kv_launch(P, theta, batch_size, stream, "launch_rope_batch");
+}
+// The engine's batched store writes every sequence into ONE cache at its position
+// (engine/kernels.hip:784-788); s12_store_kv_batch below adds the per-sequence stride.
+int s12_store_kv_batch(const float* k, const float* v, int8_t* kv_k, int8_t* kv_v, float* kv_scale_k, float* kv_scale_v,
+                       const int* positions, int n_head_kv, int head_dim, long long kv_stride, int batch_size, void* stream)
+{
+    if (!k || !v || !kv_k || !kv_v || !kv_scale_k || !kv_scale_v || !positions) return fail(S12_ERR_BAD_ARG, "store_kv_batch: null argument");
+    RopeKvParams P = {};
+    P.k = const_cast<float*>(k); P.v = v; P.kv_k = kv_k; P.kv_v = kv_v; P.sc_k = kv_scale_k; P.sc_v = kv_scale_v;
+    P.positions = positions; P.head_dim = head_dim; P.n_head = 0; P.n_head_kv = n_head_kv;
+    P.k_stride = n_head_kv * head_dim; P.kv_stride = kv_stride; P.rope = 0; P.store = 1;
+    return rope_kv_launch(P, 10000.0f, batch_size, stream, "store_kv_batch");
+}
+int launch_store_kv_batch(const float* k, const float* v, int8_t* kv_k, int8_t* kv_v, float* kv_scale_k, float* kv_scale_v,
+                          const int* positions, int kv_dim, int max_seq, int n_head_kv, int head_dim, int batch_size, void* stream)
+{
+    (void)kv_dim; (void)max_seq;
+    return s12_store_kv_batch(k, v, kv_k, kv_v, kv_scale_k, kv_scale_v, positions, n_head_kv, head_dim, 0, batch_size, stream);
+}
+
+int launch_attention_all_heads(const float* q, const int8_t* k_cache, const int8_t* v_cache, const float* kv_scale_k,
+                               const float* kv_scale_v, int16_t* output, int n_head, int n_head_kv, int head_dim, int seq_len,
+                               int max_seq, float scale, void* stream)
+{
+    (void)max_seq;
+    if (!q || !k_cache || !v_cache || !kv_scale_k || !kv_scale_v || !output) return fail(S12_ERR_BAD_ARG, "launch_attention_all_heads: null argument");
+    AttnParams P = {};
+    P.scale = scale;
+    P.q = q; P.kc = k_cache; P.vc = v_cache; P.sk = kv_scale_k; P.sv = kv_scale_v; P.out = output;
+    P.seq_len = seq_len; P.n_head = n_head; P.n_head_kv = n_head_kv; P.head_dim = head_dim;
+    return attention_launch(P, seq_len, 1, stream, "launch_attention_all_heads");
+}
+int launch_attention_all_heads_batch(const float* q, const int8_t* kv_k, const int8_t* kv_v, const float* kv_scale_k,
+                                     const float* kv_scale_v, int16_t* output, const int* positions, int n_head, int n_head_kv,
+                                     int head_dim, int max_seq, float scale, int batch_size, int kv_stride, void* stream)
+{
+    if (!q || !kv_k || !kv_v || !kv_scale_k || !kv_scale_v || !output || !positions)
+        return fail(S12_ERR_BAD_ARG, "launch_attention_all_heads_batch: null argument");
+    AttnParams P = {};
+    P.scale = scale;
+    P.q = q; P.kc = kv_k; P.vc = kv_v; P.sk = kv_scale_k; P.sv = kv_scale_v; P.out = output; P.positions = positions;
+    P.n_head = n_head; P.n_head_kv = n_head_kv; P.head_dim = head_dim; P.kv_stride = kv_stride;
+    return attention_launch(P, max_seq, batch_size, stream, "launch_attention_all_heads_batch");   // max_seq: largest position + 1
+}
+
+}  // extern "C"

@@ -309,6 +309,69 @@ class Split12Engine:
         check(self.lib.s12_decompress_async(C.byref(t), _ptr(out), _stream(stream)), "s12_decompress_async")
         return out
 
+    # ---- the decode step around the projections (engine/kernels.hip launchers, same argument order) ----
+    def embed_lookup(self, table_bf16: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor, stream=None) -> None:
+        n_vocab, n_embd = table_bf16.shape
+        check(self.lib.launch_embed_lookup(_ptr(table_bf16), _ptr(token_ids), _ptr(out), n_embd, token_ids.numel(),
+                                           n_vocab, _stream(stream)), "launch_embed_lookup")
+
+    def argmax(self, logits: torch.Tensor, result: torch.Tensor, stream=None) -> None:
+        batch, n = (1, logits.numel()) if logits.dim() == 1 else logits.shape
+        check(self.lib.launch_argmax_batch(_ptr(logits), _ptr(result), n, batch, _stream(stream)), "launch_argmax_batch")
+
+    def rms_norm_bf16(self, x: torch.Tensor, weight: torch.Tensor, y_bf16: torch.Tensor, eps: float, batch: int = 1,
+                      residual: Optional[torch.Tensor] = None, stream=None) -> None:
+        n = weight.numel()
+        if residual is None:
+            check(self.lib.launch_rms_norm_bf16_batch(_ptr(x), _ptr(weight), _ptr(y_bf16), n, eps, batch, _stream(stream)),
+                  "launch_rms_norm_bf16_batch")
+        else:                                  # x += residual in place, then the norm of the sum
+            check(self.lib.launch_add_rms_norm_bf16_batch(_ptr(x), _ptr(residual), _ptr(weight), _ptr(y_bf16), n, eps,
+                                                          batch, _stream(stream)), "launch_add_rms_norm_bf16_batch")
+
+    def silu_mul_bf16(self, gate: torch.Tensor, up: torch.Tensor, out_bf16: torch.Tensor, n: int, batch: int = 1,
+                      stream=None) -> None:
+        check(self.lib.launch_silu_mul_bf16_batch(_ptr(gate), _ptr(up), _ptr(out_bf16), n, batch, _stream(stream)),
+              "launch_silu_mul_bf16_batch")
+
+    def add(self, y: torch.Tensor, x: torch.Tensor, n: int, batch: int = 1, stream=None) -> None:
+        check(self.lib.launch_add_batch(_ptr(y), _ptr(x), n, batch, _stream(stream)), "launch_add_batch")
+
+    def rope_store_kv(self, q, k, v, kv_k, kv_v, scale_k, scale_v, head_dim: int, n_head: int, n_head_kv: int,
+                      position: int, max_seq: int, theta: float, stream=None) -> None:
+        check(self.lib.launch_rope_store_kv(_ptr(q), _ptr(k), _ptr(v), _ptr(kv_k), _ptr(kv_v), _ptr(scale_k), _ptr(scale_v),
+                                            head_dim, n_head, n_head_kv, position, max_seq, theta, _stream(stream)),
+              "launch_rope_store_kv")
+
+    def rope_batch(self, q, k, positions, head_dim: int, n_head: int, n_head_kv: int, theta: float, batch: int,
+                   stream=None) -> None:
+        check(self.lib.launch_rope_batch(_ptr(q), _ptr(k), _ptr(positions), head_dim, n_head, n_head_kv, n_head * head_dim,
+                                         n_head_kv * head_dim, theta, batch, _stream(stream)), "launch_rope_batch")
+
+    def store_kv_batch(self, k, v, kv_k, kv_v, scale_k, scale_v, positions, n_head_kv: int, head_dim: int, batch: int,
+                       kv_stride: int = 0, max_seq: int = 0, stream=None) -> None:
+        if kv_stride == 0:
+            check(self.lib.launch_store_kv_batch(_ptr(k), _ptr(v), _ptr(kv_k), _ptr(kv_v), _ptr(scale_k), _ptr(scale_v),
+                                                 _ptr(positions), n_head_kv * head_dim, max_seq, n_head_kv, head_dim, batch,
+                                                 _stream(stream)), "launch_store_kv_batch")
+        else:
+            check(self.lib.s12_store_kv_batch(_ptr(k), _ptr(v), _ptr(kv_k), _ptr(kv_v), _ptr(scale_k), _ptr(scale_v),
+                                              _ptr(positions), n_head_kv, head_dim, kv_stride, batch, _stream(stream)),
+                  "s12_store_kv_batch")
+
+    def attention_all_heads(self, q, kv_k, kv_v, scale_k, scale_v, out_bf16, n_head: int, n_head_kv: int, head_dim: int,
+                            seq_len: int, max_seq: int, scale: float, stream=None) -> None:
+        check(self.lib.launch_attention_all_heads(_ptr(q), _ptr(kv_k), _ptr(kv_v), _ptr(scale_k), _ptr(scale_v),
+                                                  _ptr(out_bf16), n_head, n_head_kv, head_dim, seq_len, max_seq, scale,
+                                                  _stream(stream)), "launch_attention_all_heads")
+
+    def attention_all_heads_batch(self, q, kv_k, kv_v, scale_k, scale_v, out_bf16, positions, n_head: int, n_head_kv: int,
+                                  head_dim: int, max_len: int, scale: float, batch: int, kv_stride: int, stream=None) -> None:
+        check(self.lib.launch_attention_all_heads_batch(_ptr(q), _ptr(kv_k), _ptr(kv_v), _ptr(scale_k), _ptr(scale_v),
+                                                        _ptr(out_bf16), _ptr(positions), n_head, n_head_kv, head_dim, max_len,
+                                                        scale, batch, kv_stride, _stream(stream)),
+              "launch_attention_all_heads_batch")
+
     def set_dependent_launch(self, enable: bool) -> bool:
         return bool(self.lib.s12_set_dependent_launch(1 if enable else 0))
 
