@@ -39,6 +39,16 @@ WORKLOADS = {
                          desc="Llama-3.1-8B-shaped decode step at B=256 (BASELINE configs[2]): all split12 projections"),
     "llama70b_b1": dict(layers=80, hidden=8192, q=8192, kv=1024, ffn=28672, vocab=128256, batch=1,
                         desc="Llama-3-70B-shaped decode step at B=1 (BASELINE configs[3]): all split12 projections"),
+    # the whole decode step (engine/inference.cpp forward loop): the projections plus embed, norms, RoPE + INT8
+    # KV store, attention at a mid-generation position, SiLU*up, argmax -- what the reference's tok/s measures
+    "mistral7b_b1_full": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=32000, batch=1, full=True,
+                              heads=32, kv_heads=8, position=255, max_seq=384,
+                              desc="Mistral-7B-shaped greedy decode step at B=1, every kernel of the step, at position 255 "
+                                   "(128-token prompt + 256 generated, BASELINE configs[1])"),
+    "llama8b_b256_full": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=128256, batch=256, full=True,
+                              heads=32, kv_heads=8, position=191, max_seq=256,
+                              desc="Llama-3.1-8B-shaped greedy decode step at B=256, every kernel of the step, at position "
+                                   "191 (128-token prompts + 128 generated, BASELINE configs[2])"),
     "config1": dict(layers=32, hidden=4096, q=4096, kv=0, ffn=0, vocab=0, batch=1,
                     desc="32 distinct 4096x4096 tensors with 0.05% x100 outliers (BASELINE configs[0] shape), one GEMV each"),
 }
@@ -423,6 +433,109 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_full(args):
+    """Whole decode step through turbo_lossless_b200.decoder.Decoder, one GPU."""
+    import torch
+    from turbo_lossless_b200 import CompressedWeight, Decoder, DecoderConfig, Split12Engine
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"unavailable": "the *_full workloads run on one GPU"}), flush=True)
+        return
+    torch.cuda.set_device(0)
+    cfg = WORKLOADS[args.workload]
+    layers = args.layers or cfg["layers"]
+    B, H, V = cfg["batch"], cfg["hidden"], cfg["vocab"]
+    eng = Split12Engine()
+    model = build_model(cfg, 0, 1, layers, torch, CompressedWeight)
+    tensors = model_tensors(model)
+    total_bytes = float(sum(t.compressed_bytes for t in tensors))
+    total_weights = float(sum(t.M * t.K for t in tensors))
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(11)
+    dc = DecoderConfig(n_embd=H, n_head=cfg["heads"], n_head_kv=cfg["kv_heads"], n_ff=cfg["ffn"], n_vocab=V, n_layer=layers,
+                       max_seq=cfg["max_seq"])
+    embd = torch.randn(V, H, generator=gen, device=dev).to(torch.bfloat16).view(torch.int16)
+    names = [f"attn_norm.{i}" for i in range(layers)] + [f"ffn_norm.{i}" for i in range(layers)] + ["output_norm"]
+    norms = {nm: 1.0 + 0.1 * torch.randn(H, generator=gen, device=dev) for nm in names}
+    dec = Decoder(dc, model["layers"], model["lm_head"], embd, norms, batch=B, eng=eng)
+    # a cache that looks like `position` earlier steps: random int8 entries and scales of the size real keys give
+    pos = cfg["position"]
+    dec.kv_k.copy_(torch.randint(-127, 128, dec.kv_k.shape, generator=gen, device=dev, dtype=torch.int8))
+    dec.kv_v.copy_(torch.randint(-127, 128, dec.kv_v.shape, generator=gen, device=dev, dtype=torch.int8))
+    dec.sc_k.fill_(0.02); dec.sc_v.fill_(0.02)
+    dec.positions.fill_(pos)
+    tok_host = torch.randint(0, V, (B,), dtype=torch.int32).pin_memory()
+    out_host = torch.zeros(B, dtype=torch.int32).pin_memory()
+    dec.tokens.copy_(tok_host)
+    eng.set_dependent_launch(not args.no_pdl)
+    stream = torch.cuda.Stream()
+    graph = None
+    with torch.cuda.stream(stream):
+        dec.forward(attn_len=pos + 1)
+        torch.cuda.synchronize()
+        if not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                dec.forward(attn_len=pos + 1)
+        run = graph.replay if graph is not None else (lambda: dec.forward(attn_len=pos + 1))
+        for _ in range(args.warmup):
+            run()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        # end to end: token ids in from pinned host memory, the greedy tokens back, every step
+        for _ in range(2):
+            dec.tokens.copy_(tok_host, non_blocking=True); run(); out_host.copy_(dec.next_tokens, non_blocking=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            dec.tokens.copy_(tok_host, non_blocking=True)
+            run()
+            out_host.copy_(dec.next_tokens, non_blocking=True)
+            stream.synchronize()
+        e2e_s = time.perf_counter() - t0
+    status = eng.device_status()
+    hbm_peak, tf_peak, peak_src = peaks()
+    ms_step = ms / args.steps
+    gbs = total_bytes / (ms_step * 1e-3) / 1e9
+    if B >= 128:
+        achieved = 2.0 * total_weights * B / (ms_step * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": round(achieved, 2), "peak": tf_peak, "unit": "TFLOP/s",
+                "frac": round(achieved / tf_peak, 4), "kernel": "gemm_tc_kernel"}
+    else:
+        roof = {"bound": "hbm", "achieved": round(gbs, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(gbs / hbm_peak, 4),
+                "kernel": "gemv_stream_kernel"}
+    ratio = TRAFFIC_RATIO.get(roof["kernel"])
+    roof["traffic"] = int(total_bytes * ratio) if ratio else None
+    roof["peak_source"] = f"{peak_src} (MEASURED_PEAKS.json)" if peak_src == "measured" else "fallback"
+    roof["note"] = "projection bytes / flops over the time of the WHOLE step (attention, norms, ... included in the time only)"
+    roof["algorithmic_bytes_per_step"] = int(total_bytes)
+    line = {
+        "metric": "tok/s", "value": round(B * args.steps / (ms / 1e3), 2), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16 weights (split12), fp32 accumulate, int8 KV cache",
+        "data": "synthetic: seeded N(0,0.02) bf16 weights packed to split12 on the device; random embeddings, norms, tokens "
+                "and a random int8 KV cache of `position` entries",
+        "config": {"workload": args.workload, "what": cfg["desc"], "layers": layers, "batch": B, "parallelism": "single",
+                   "position": pos, "l2": "inputs larger than L2 (packed weights of one step: %.2f GB)" % (total_bytes / 1e9),
+                   "launch": ("cuda graph" if graph is not None else "eager") + ("" if args.no_pdl else " + programmatic dependent launch")},
+        "compressed_GBps_per_gpu": round(gbs, 1), "roofline": roof,
+        "e2e": {"value": round(B * args.steps / e2e_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": dec.launches_per_step() * args.steps, "clocks": clocks, "device_status": status,
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(cfg, layers, total_weights, B, seconds=12.0)
+    print(json.dumps(line), flush=True)
+
+
 # ----------------------------------------------------------------------------------------------
 # CPU statement of the path (oracle port), used as the reported baseline and as the reference arm
 # ----------------------------------------------------------------------------------------------
@@ -490,5 +603,7 @@ if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif WORKLOADS[a.workload].get("full"):
+        run_full(a)
     else:
         run_ours(a)

@@ -90,6 +90,28 @@ rms_norm_kernel(float* __restrict__ x, const float* __restrict__ residual, const
     grid_dependency_wait();
     const size_t off = (size_t)blockIdx.x * n;
     float ss = 0.f;
+    const bool vec = (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
+                                       (kAdd ? reinterpret_cast<uintptr_t>(residual) : 0)) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(y) & 7) == 0;
+    if (vec) {                                                    // 16-byte aligned rows: four elements per load
+        float4* x4 = reinterpret_cast<float4*>(x + off);
+        const float4* r4 = reinterpret_cast<const float4*>(residual + (kAdd ? off : 0));
+        for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            float4 v = x4[i];
+            if (kAdd) { const float4 r = r4[i]; v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w; x4[i] = v; }
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_reduce<false>(ss, scratch);
+        const float rms = rsqrtf(ss / (float)n + eps);
+        const float4* w4 = reinterpret_cast<const float4*>(weight);
+        for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            const float4 v = x4[i], w = w4[i];                    // a thread re-reads only what it wrote
+            const uint32_t lo = (uint16_t)float_to_bf16_rne(v.x * rms * w.x) | ((uint32_t)(uint16_t)float_to_bf16_rne(v.y * rms * w.y) << 16);
+            const uint32_t hi = (uint16_t)float_to_bf16_rne(v.z * rms * w.z) | ((uint32_t)(uint16_t)float_to_bf16_rne(v.w * rms * w.w) << 16);
+            reinterpret_cast<uint2*>(y + off)[i] = make_uint2(lo, hi);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = x[off + i];
         if (kAdd) { v += residual[off + i]; x[off + i] = v; }
@@ -201,11 +223,14 @@ rope_kv_kernel(const __grid_constant__ RopeKvParams P, const __grid_constant__ R
 // ---------------------------------------------------------------------------
 // Decode attention over the INT8 cache (engine/kernels.hip:499-586, 606-692):
 // scores[t] = scale * sum_d q[d] * (k[t][d] * sk[t]); softmax over t <= pos;
-// out[d] = sum_t p[t] * (v[t][d] * sv[t]) -> bf16.  CTA = (q head, sequence),
-// 8 warps.  Scores: one warp per position, a lane holds four q values and
-// reads four int8 of the key row (128 contiguous bytes per warp).  Values:
-// thread (g, d) sums over its share of the positions, 128 contiguous bytes per
-// warp and position; the shares are added through shared memory.
+// out[d] = sum_t p[t] * (v[t][d] * sv[t]) -> bf16.
+// CTA = (kv head, sequence), 8 warps: the key and value rows of a kv head are
+// read once for all the query heads that share it (GQA).  Both passes walk the
+// positions one warp per position, a lane reading four consecutive int8 of the
+// row (128 contiguous bytes per warp for head_dim 128), four positions in
+// flight per warp; a lane keeps its four q values of every query head in
+// registers, and the value pass accumulates per lane and is added across the
+// warps through shared memory.
 // ---------------------------------------------------------------------------
 struct AttnParams {
     const float* q; const int8_t* kc; const int8_t* vc; const float* sk; const float* sv;
@@ -215,94 +240,154 @@ struct AttnParams {
     int n_head, n_head_kv, head_dim;
     long long kv_stride;
     float scale;
+    int score_stride;           // floats between the score rows of two query heads in shared memory
 };
 
 constexpr int kAttnThreads = 256;
+constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnMaxGqa = 8;           // query heads per kv head
 
+__device__ __forceinline__ void unpack_s8x4(int w, float (&f)[4])
+{
+    f[0] = (float)(int8_t)(w & 0xFF); f[1] = (float)(int8_t)((w >> 8) & 0xFF);
+    f[2] = (float)(int8_t)((w >> 16) & 0xFF); f[3] = (float)(int8_t)(w >> 24);
+}
+
+template <int kGqa, int kChunks>         // kChunks: 128-element pieces of a head (head_dim <= 128 * kChunks)
 __global__ void __launch_bounds__(kAttnThreads)
 attention_kernel(const __grid_constant__ AttnParams P)
 {
-    extern __shared__ float att_smem[];                           // scores[seq_len], then acc[groups][head_dim]
+    extern __shared__ float att_smem[];                           // scores[kGqa][score_stride], then acc[warps][kGqa][head_dim]
     __shared__ float scratch[33];
     grid_launch_dependents();
     grid_dependency_wait();
-    const int head = blockIdx.x, seq = blockIdx.y;
-    const int hd = P.head_dim, kvh = head / (P.n_head / P.n_head_kv);
-    const int T = P.positions ? P.positions[seq] + 1 : P.seq_len;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = kAttnThreads / 32;
+    const int kvh = blockIdx.x, seq = blockIdx.y;
+    const int hd = P.head_dim;
+    const int Tw = P.positions ? P.positions[seq] + 1 : P.seq_len;
+    const int T = Tw < P.score_stride ? Tw : P.score_stride;      // never past the score rows this launch was sized for
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t kv_dim = (size_t)P.n_head_kv * hd;
     const int8_t* kc = P.kc + (size_t)seq * P.kv_stride + (size_t)kvh * hd;
     const int8_t* vc = P.vc + (size_t)seq * P.kv_stride + (size_t)kvh * hd;
     const float* sk = P.sk + (size_t)seq * (P.kv_stride / hd) + kvh;
     const float* sv = P.sv + (size_t)seq * (P.kv_stride / hd) + kvh;
-    const float* q = P.q + ((size_t)seq * P.n_head + head) * hd;
+    const float* q = P.q + ((size_t)seq * P.n_head + (size_t)kvh * kGqa) * hd;
     float* scores = att_smem;
-    float* accs = att_smem + ((T + 3) & ~3);
-    const float scale = P.scale;
+    float* accs = att_smem + (size_t)kGqa * P.score_stride;
+    const int ss = P.score_stride;
 
-    // scores: lane owns elements [4*lane + 128*j, +4) of the head
-    const int chunks = (hd + 127) / 128;
-    float qv[2][4];
+    // a lane owns elements [128*c + 4*lane, +4) of the head, c < kChunks
+    bool live[kChunks];
+    float qv[kGqa][kChunks][4];
 #pragma unroll
-    for (int j = 0; j < 2; j++)
+    for (int c = 0; c < kChunks; c++) {
+        live[c] = c * 128 + lane * 4 < hd;                        // head_dim is a multiple of 4
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int d = j * 128 + lane * 4 + e;
-            qv[j][e] = (j < chunks && d < hd) ? q[d] : 0.f;
+        for (int h = 0; h < kGqa; h++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) qv[h][c][e] = live[c] ? q[(size_t)h * hd + c * 128 + lane * 4 + e] : 0.f;
+    }
+    // ---- scores
+    for (int t0 = warp; t0 < T; t0 += 4 * kAttnWarps) {
+        int w[4][kChunks];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int t = t0 + u * kAttnWarps;
+#pragma unroll
+            for (int c = 0; c < kChunks; c++)
+                w[u][c] = (t < T && live[c]) ? *reinterpret_cast<const int*>(kc + (size_t)t * kv_dim + c * 128 + lane * 4) : 0;
         }
-    for (int t = warp; t < T; t += nwarps) {
-        const int8_t* row = kc + (size_t)t * kv_dim;
-        float dot = 0.f;
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            if (j >= chunks) break;
-            const int d0 = j * 128 + lane * 4;
-            if (d0 + 3 < hd) {
-                const int w = *reinterpret_cast<const int*>(row + d0);       // rows start on multiples of head_dim (>= 4)
-                dot += qv[j][0] * (float)(int8_t)(w & 0xFF) + qv[j][1] * (float)(int8_t)((w >> 8) & 0xFF) +
-                       qv[j][2] * (float)(int8_t)((w >> 16) & 0xFF) + qv[j][3] * (float)(int8_t)(w >> 24);
-            } else {
-                for (int e = 0; e < 4; e++)
-                    if (d0 + e < hd) dot += qv[j][e] * (float)row[d0 + e];
+        for (int u = 0; u < 4; u++) {
+            const int t = t0 + u * kAttnWarps;
+            float dot[kGqa];
+#pragma unroll
+            for (int h = 0; h < kGqa; h++) dot[h] = 0.f;
+#pragma unroll
+            for (int c = 0; c < kChunks; c++) {
+                float kf[4];
+                unpack_s8x4(w[u][c], kf);
+#pragma unroll
+                for (int h = 0; h < kGqa; h++)
+                    dot[h] += qv[h][c][0] * kf[0] + qv[h][c][1] * kf[1] + qv[h][c][2] * kf[2] + qv[h][c][3] * kf[3];
+            }
+#pragma unroll
+            for (int h = 0; h < kGqa; h++)
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) dot[h] += __shfl_xor_sync(0xFFFFFFFFu, dot[h], off);
+            if (t < T && lane < kGqa) {
+                float mine = dot[0];
+#pragma unroll
+                for (int h = 1; h < kGqa; h++) mine = lane == h ? dot[h] : mine;
+                scores[lane * ss + t] = mine * sk[(size_t)t * P.n_head_kv] * P.scale;
             }
         }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, off);
-        if (lane == 0) scores[t] = dot * sk[(size_t)t * P.n_head_kv] * scale;
     }
     __syncthreads();
-    float m = -1e30f;
-    for (int t = threadIdx.x; t < T; t += kAttnThreads) m = fmaxf(m, scores[t]);
-    m = block_reduce<true>(m, scratch);
-    float sum = 0.f;
-    for (int t = threadIdx.x; t < T; t += kAttnThreads) {
-        const float e = expf(scores[t] - m);
-        scores[t] = e * sv[(size_t)t * P.n_head_kv];              // fold the value scale into the weight
-        sum += e;
+    // ---- softmax per query head; the value scale is folded into the weight
+    float inv[kGqa];
+#pragma unroll
+    for (int h = 0; h < kGqa; h++) {
+        float m = -1e30f;
+        for (int t = threadIdx.x; t < T; t += kAttnThreads) m = fmaxf(m, scores[h * ss + t]);
+        m = block_reduce<true>(m, scratch);
+        float sum = 0.f;
+        for (int t = threadIdx.x; t < T; t += kAttnThreads) {
+            const float e = expf(scores[h * ss + t] - m);
+            scores[h * ss + t] = e * sv[(size_t)t * P.n_head_kv];
+            sum += e;
+        }
+        inv[h] = 1.0f / block_reduce<false>(sum, scratch);
     }
-    sum = block_reduce<false>(sum, scratch);
-    const float inv = 1.0f / sum;
-
-    // values: group g of threads takes positions g, g + groups, ...
-    const int groups = kAttnThreads / hd > 0 ? kAttnThreads / hd : 1;
-    const int g = threadIdx.x / hd, d = threadIdx.x % hd;
-    if (hd <= kAttnThreads) {
-        float acc = 0.f;
-        if (g < groups)
-            for (int t = g; t < T; t += groups) acc += scores[t] * (float)vc[(size_t)t * kv_dim + d];
-        if (g < groups) accs[g * hd + d] = acc;
-        __syncthreads();
-        if (threadIdx.x < hd) {
-            float a = 0.f;
-            for (int gg = 0; gg < groups; gg++) a += accs[gg * hd + threadIdx.x];
-            P.out[((size_t)seq * P.n_head + head) * hd + threadIdx.x] = float_to_bf16_rne(a * inv);
+    // ---- values
+    float acc[kGqa][kChunks][4];
+#pragma unroll
+    for (int h = 0; h < kGqa; h++)
+#pragma unroll
+        for (int c = 0; c < kChunks; c++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[h][c][e] = 0.f;
+    for (int t0 = warp; t0 < T; t0 += 4 * kAttnWarps) {
+        int w[4][kChunks];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int t = t0 + u * kAttnWarps;
+#pragma unroll
+            for (int c = 0; c < kChunks; c++)
+                w[u][c] = (t < T && live[c]) ? *reinterpret_cast<const int*>(vc + (size_t)t * kv_dim + c * 128 + lane * 4) : 0;
         }
-    } else {
-        for (int dd = threadIdx.x; dd < hd; dd += kAttnThreads) {
-            float acc = 0.f;
-            for (int t = 0; t < T; t++) acc += scores[t] * (float)vc[(size_t)t * kv_dim + dd];
-            P.out[((size_t)seq * P.n_head + head) * hd + dd] = float_to_bf16_rne(acc * inv);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int t = t0 + u * kAttnWarps;
+            if (t >= T) break;
+            float p[kGqa];
+#pragma unroll
+            for (int h = 0; h < kGqa; h++) p[h] = scores[h * ss + t];
+#pragma unroll
+            for (int c = 0; c < kChunks; c++) {
+                float vf[4];
+                unpack_s8x4(w[u][c], vf);
+#pragma unroll
+                for (int h = 0; h < kGqa; h++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) acc[h][c][e] += p[h] * vf[e];
+            }
         }
+    }
+#pragma unroll
+    for (int h = 0; h < kGqa; h++)
+#pragma unroll
+        for (int c = 0; c < kChunks; c++)
+            if (live[c])
+                *reinterpret_cast<float4*>(accs + ((size_t)warp * kGqa + h) * hd + c * 128 + lane * 4) =
+                    make_float4(acc[h][c][0], acc[h][c][1], acc[h][c][2], acc[h][c][3]);
+    __syncthreads();
+    for (int i = threadIdx.x; i < kGqa * hd; i += kAttnThreads) {
+        const int h = i / hd, d = i - h * hd;
+        float a = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < kAttnWarps; wv++) a += accs[((size_t)wv * kGqa + h) * hd + d];
+        P.out[((size_t)seq * P.n_head + (size_t)kvh * kGqa + h) * hd + d] = float_to_bf16_rne(a * inv[h]);
     }
 }
 
@@ -333,9 +418,25 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ result, int n)
     const float* row = logits + (size_t)blockIdx.x * n;
     float bv = -INFINITY;
     int bi = 0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = row[i];
-        if (argmax_better(v, i, bv, bi)) { bv = v; bi = i; }
+    if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {   // 16-byte aligned rows: four elements per load, two in flight
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        for (int i = threadIdx.x; i < n / 4; i += 2 * blockDim.x) {
+            const int j = i + blockDim.x;
+            const float4 a = r4[i];
+            const float4 b = j < n / 4 ? r4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            const float va[4] = {a.x, a.y, a.z, a.w}, vb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) if (argmax_better(va[e], 4 * i + e, bv, bi)) { bv = va[e]; bi = 4 * i + e; }
+            if (j < n / 4) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) if (argmax_better(vb[e], 4 * j + e, bv, bi)) { bv = vb[e]; bi = 4 * j + e; }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = row[i];
+            if (argmax_better(v, i, bv, bi)) { bv = v; bi = i; }
+        }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -396,21 +497,29 @@ static int attention_launch(AttnParams& P, int max_len, int batch, void* stream,
     if (P.head_dim < 4 || P.head_dim > 256 || (P.head_dim & 3) || P.n_head_kv < 1 || P.n_head < P.n_head_kv ||
         P.n_head % P.n_head_kv != 0 || max_len < 1 || batch < 1)
         return fail(S12_ERR_UNSUPPORTED, "%s: needs head_dim %% 4 == 0 and <= 256, n_head a multiple of n_head_kv, seq_len >= 1", who);
-    const int groups = kAttnThreads / P.head_dim > 0 ? kAttnThreads / P.head_dim : 1;
-    const size_t smem = ((size_t)((max_len + 3) & ~3) + (size_t)groups * P.head_dim) * sizeof(float);
+    const int gqa = P.n_head / P.n_head_kv;
+    if (gqa != 1 && gqa != 2 && gqa != 4 && gqa != 8)
+        return fail(S12_ERR_UNSUPPORTED, "%s: %d query heads per kv head (supported: 1, 2, 4, 8)", who, gqa);
+    P.score_stride = (max_len + 3) & ~3;
+    const size_t smem = ((size_t)gqa * P.score_stride + (size_t)kAttnWarps * gqa * P.head_dim) * sizeof(float);
     if (smem > 200 * 1024) return fail(S12_ERR_TOO_LARGE, "%s: seq_len %d needs more shared memory than one CTA has", who, max_len);
-    static bool attr_set[64];
+    typedef void (*Kern)(const AttnParams);
+    static const Kern table[4][2] = {{attention_kernel<1, 1>, attention_kernel<1, 2>}, {attention_kernel<2, 1>, attention_kernel<2, 2>},
+                                     {attention_kernel<4, 1>, attention_kernel<4, 2>}, {attention_kernel<8, 1>, attention_kernel<8, 2>}};
+    const int gi = gqa == 1 ? 0 : gqa == 2 ? 1 : gqa == 4 ? 2 : 3, ci = P.head_dim > 128 ? 1 : 0;
+    Kern kern = table[gi][ci];
+    static bool attr_set[64][4][2];
     if (smem > 48 * 1024) {
         int dev = 0;
         cudaGetDevice(&dev);
         dev = (dev < 0 || dev >= 64) ? 0 : dev;
-        if (!attr_set[dev]) {
-            int rc = check_cuda(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), who);
+        if (!attr_set[dev][gi][ci]) {
+            int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), who);
             if (rc) return rc;
-            attr_set[dev] = true;
+            attr_set[dev][gi][ci] = true;
         }
     }
-    return launch(attention_kernel, dim3(P.n_head, batch), dim3(kAttnThreads), smem, stream, who, P);
+    return launch(kern, dim3(P.n_head_kv, batch), dim3(kAttnThreads), smem, stream, who, P);
 }
 
 }  // namespace s12
