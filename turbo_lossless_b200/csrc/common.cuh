@@ -49,6 +49,31 @@ int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* s
 {
     return launch_clustered(kernel, grid, block, smem, stream, name, 1, args...);
 }
+// clusters along the grid's z dimension
+template <typename... KArgs, typename... Args>
+int launch_clustered_z(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
+                       const char* name, int cluster_z, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (dependent_launch_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        n++;
+    }
+    cfg.attrs = attr; cfg.numAttrs = (unsigned)n;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...), name);
+}
 
 // ---------------------------------------------------------------------------
 // PTX wrappers

@@ -224,13 +224,16 @@ rope_kv_kernel(const __grid_constant__ RopeKvParams P, const __grid_constant__ R
 // Decode attention over the INT8 cache (engine/kernels.hip:499-586, 606-692):
 // scores[t] = scale * sum_d q[d] * (k[t][d] * sk[t]); softmax over t <= pos;
 // out[d] = sum_t p[t] * (v[t][d] * sv[t]) -> bf16.
-// CTA = (kv head, sequence), 8 warps: the key and value rows of a kv head are
-// read once for all the query heads that share it (GQA).  Both passes walk the
-// positions one warp per position, a lane reading four consecutive int8 of the
-// row (128 contiguous bytes per warp for head_dim 128), four positions in
-// flight per warp; a lane keeps its four q values of every query head in
-// registers, and the value pass accumulates per lane and is added across the
-// warps through shared memory.
+// CTA = (kv head, sequence, slice of the positions), 8 warps: the key and value
+// rows of a kv head are read once for all the query heads that share it (GQA).
+// Both passes walk the positions one warp per position, a lane reading four
+// consecutive int8 of the row (128 contiguous bytes per warp for head_dim 128),
+// eight positions in flight per warp; a lane keeps its four q values of every
+// query head in registers.  Softmax statistics are per query head and per
+// slice (one warp per head, shuffles only).  With few sequences the positions
+// are cut into slices that run as one thread-block cluster, and the slices'
+// (max, sum, weighted values) are merged over distributed shared memory --
+// split-KV decoding without a second kernel or a workspace.
 // ---------------------------------------------------------------------------
 struct AttnParams {
     const float* q; const int8_t* kc; const int8_t* vc; const float* sk; const float* sv;
@@ -241,30 +244,49 @@ struct AttnParams {
     long long kv_stride;
     float scale;
     int score_stride;           // floats between the score rows of two query heads in shared memory
+    int nsplit;                 // CTAs (= cluster size) that share the positions of one (kv head, sequence)
 };
 
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
-constexpr int kAttnMaxGqa = 8;           // query heads per kv head
+constexpr int kAttnFlight = 8;           // positions in flight per warp
 
 __device__ __forceinline__ void unpack_s8x4(int w, float (&f)[4])
 {
     f[0] = (float)(int8_t)(w & 0xFF); f[1] = (float)(int8_t)((w >> 8) & 0xFF);
     f[2] = (float)(int8_t)((w >> 16) & 0xFF); f[3] = (float)(int8_t)(w >> 24);
 }
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr)
+{
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t dsmem_addr(const void* p, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 template <int kGqa, int kChunks>         // kChunks: 128-element pieces of a head (head_dim <= 128 * kChunks)
 __global__ void __launch_bounds__(kAttnThreads)
 attention_kernel(const __grid_constant__ AttnParams P)
 {
-    extern __shared__ float att_smem[];                           // scores[kGqa][score_stride], then acc[warps][kGqa][head_dim]
-    __shared__ float scratch[33];
+    // scores[kGqa][score_stride], acc[warps][kGqa][head_dim] (reused as the slice's sum [kGqa][head_dim]), stats[2][kGqa]
+    extern __shared__ float att_smem[];
     grid_launch_dependents();
     grid_dependency_wait();
-    const int kvh = blockIdx.x, seq = blockIdx.y;
+    const int kvh = blockIdx.x, seq = blockIdx.y, split = blockIdx.z, nsplit = P.nsplit;
     const int hd = P.head_dim;
     const int Tw = P.positions ? P.positions[seq] + 1 : P.seq_len;
-    const int T = Tw < P.score_stride ? Tw : P.score_stride;      // never past the score rows this launch was sized for
+    const int T = Tw < P.score_stride * nsplit ? Tw : P.score_stride * nsplit;   // never past what this launch was sized for
+    const int per = (T + nsplit - 1) / nsplit;
+    const int t_lo = split * per, t_hi = t_lo + per < T ? t_lo + per : T;       // this CTA's positions
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t kv_dim = (size_t)P.n_head_kv * hd;
     const int8_t* kc = P.kc + (size_t)seq * P.kv_stride + (size_t)kvh * hd;
@@ -272,9 +294,10 @@ attention_kernel(const __grid_constant__ AttnParams P)
     const float* sk = P.sk + (size_t)seq * (P.kv_stride / hd) + kvh;
     const float* sv = P.sv + (size_t)seq * (P.kv_stride / hd) + kvh;
     const float* q = P.q + ((size_t)seq * P.n_head + (size_t)kvh * kGqa) * hd;
-    float* scores = att_smem;
-    float* accs = att_smem + (size_t)kGqa * P.score_stride;
     const int ss = P.score_stride;
+    float* scores = att_smem;
+    float* accs = att_smem + (size_t)kGqa * ss;
+    float* stats = accs + (size_t)kAttnWarps * kGqa * hd;        // [0][h]: slice maximum, [1][h]: slice sum of exp
 
     // a lane owns elements [128*c + 4*lane, +4) of the head, c < kChunks
     bool live[kChunks];
@@ -287,19 +310,20 @@ attention_kernel(const __grid_constant__ AttnParams P)
 #pragma unroll
             for (int e = 0; e < 4; e++) qv[h][c][e] = live[c] ? q[(size_t)h * hd + c * 128 + lane * 4 + e] : 0.f;
     }
-    // ---- scores
-    for (int t0 = warp; t0 < T; t0 += 4 * kAttnWarps) {
-        int w[4][kChunks];
+    // ---- scores of this slice (indexed from t_lo in shared memory)
+    for (int t0 = t_lo + warp; t0 < t_hi; t0 += kAttnFlight * kAttnWarps) {
+        int w[kAttnFlight][kChunks];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < kAttnFlight; u++) {
             const int t = t0 + u * kAttnWarps;
 #pragma unroll
             for (int c = 0; c < kChunks; c++)
-                w[u][c] = (t < T && live[c]) ? *reinterpret_cast<const int*>(kc + (size_t)t * kv_dim + c * 128 + lane * 4) : 0;
+                w[u][c] = (t < t_hi && live[c]) ? *reinterpret_cast<const int*>(kc + (size_t)t * kv_dim + c * 128 + lane * 4) : 0;
         }
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < kAttnFlight; u++) {
             const int t = t0 + u * kAttnWarps;
+            if (t >= t_hi) break;
             float dot[kGqa];
 #pragma unroll
             for (int h = 0; h < kGqa; h++) dot[h] = 0.f;
@@ -315,31 +339,34 @@ attention_kernel(const __grid_constant__ AttnParams P)
             for (int h = 0; h < kGqa; h++)
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) dot[h] += __shfl_xor_sync(0xFFFFFFFFu, dot[h], off);
-            if (t < T && lane < kGqa) {
+            if (lane < kGqa) {
                 float mine = dot[0];
 #pragma unroll
                 for (int h = 1; h < kGqa; h++) mine = lane == h ? dot[h] : mine;
-                scores[lane * ss + t] = mine * sk[(size_t)t * P.n_head_kv] * P.scale;
+                scores[lane * ss + (t - t_lo)] = mine * sk[(size_t)t * P.n_head_kv] * P.scale;
             }
         }
     }
     __syncthreads();
-    // ---- softmax per query head; the value scale is folded into the weight
-    float inv[kGqa];
-#pragma unroll
-    for (int h = 0; h < kGqa; h++) {
+    // ---- slice softmax, warp h for query head h; the value scale is folded into the weight
+    const int n_loc = t_hi > t_lo ? t_hi - t_lo : 0;
+    for (int h = warp; h < kGqa; h += kAttnWarps) {
         float m = -1e30f;
-        for (int t = threadIdx.x; t < T; t += kAttnThreads) m = fmaxf(m, scores[h * ss + t]);
-        m = block_reduce<true>(m, scratch);
+        for (int i = lane; i < n_loc; i += 32) m = fmaxf(m, scores[h * ss + i]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
         float sum = 0.f;
-        for (int t = threadIdx.x; t < T; t += kAttnThreads) {
-            const float e = expf(scores[h * ss + t] - m);
-            scores[h * ss + t] = e * sv[(size_t)t * P.n_head_kv];
+        for (int i = lane; i < n_loc; i += 32) {
+            const float e = expf(scores[h * ss + i] - m);
+            scores[h * ss + i] = e * sv[(size_t)(t_lo + i) * P.n_head_kv];
             sum += e;
         }
-        inv[h] = 1.0f / block_reduce<false>(sum, scratch);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+        if (lane == 0) { stats[h] = m; stats[kGqa + h] = sum; }
     }
-    // ---- values
+    __syncthreads();
+    // ---- weighted values of this slice
     float acc[kGqa][kChunks][4];
 #pragma unroll
     for (int h = 0; h < kGqa; h++)
@@ -347,22 +374,22 @@ attention_kernel(const __grid_constant__ AttnParams P)
         for (int c = 0; c < kChunks; c++)
 #pragma unroll
             for (int e = 0; e < 4; e++) acc[h][c][e] = 0.f;
-    for (int t0 = warp; t0 < T; t0 += 4 * kAttnWarps) {
-        int w[4][kChunks];
+    for (int t0 = t_lo + warp; t0 < t_hi; t0 += kAttnFlight * kAttnWarps) {
+        int w[kAttnFlight][kChunks];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < kAttnFlight; u++) {
             const int t = t0 + u * kAttnWarps;
 #pragma unroll
             for (int c = 0; c < kChunks; c++)
-                w[u][c] = (t < T && live[c]) ? *reinterpret_cast<const int*>(vc + (size_t)t * kv_dim + c * 128 + lane * 4) : 0;
+                w[u][c] = (t < t_hi && live[c]) ? *reinterpret_cast<const int*>(vc + (size_t)t * kv_dim + c * 128 + lane * 4) : 0;
         }
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < kAttnFlight; u++) {
             const int t = t0 + u * kAttnWarps;
-            if (t >= T) break;
+            if (t >= t_hi) break;
             float p[kGqa];
 #pragma unroll
-            for (int h = 0; h < kGqa; h++) p[h] = scores[h * ss + t];
+            for (int h = 0; h < kGqa; h++) p[h] = scores[h * ss + (t - t_lo)];
 #pragma unroll
             for (int c = 0; c < kChunks; c++) {
                 float vf[4];
@@ -382,13 +409,36 @@ attention_kernel(const __grid_constant__ AttnParams P)
                 *reinterpret_cast<float4*>(accs + ((size_t)warp * kGqa + h) * hd + c * 128 + lane * 4) =
                     make_float4(acc[h][c][0], acc[h][c][1], acc[h][c][2], acc[h][c][3]);
     __syncthreads();
+    // the slice's sums over its warps, in place in the first warp's rows
     for (int i = threadIdx.x; i < kGqa * hd; i += kAttnThreads) {
-        const int h = i / hd, d = i - h * hd;
         float a = 0.f;
 #pragma unroll
-        for (int wv = 0; wv < kAttnWarps; wv++) a += accs[((size_t)wv * kGqa + h) * hd + d];
-        P.out[((size_t)seq * P.n_head + (size_t)kvh * kGqa + h) * hd + d] = float_to_bf16_rne(a * inv[h]);
+        for (int wv = 0; wv < kAttnWarps; wv++) a += accs[(size_t)wv * kGqa * hd + i];
+        accs[i] = a;                                               // element i of warp 0's rows: read above by this thread only
     }
+    if (nsplit == 1) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < kGqa * hd; i += kAttnThreads) {
+            const int h = i / hd, d = i - h * hd;
+            P.out[((size_t)seq * P.n_head + (size_t)kvh * kGqa + h) * hd + d] = float_to_bf16_rne(accs[i] / stats[kGqa + h]);
+        }
+        return;
+    }
+    // ---- merge the slices of the cluster: rank r finishes the output elements i = r, r + nsplit, ...
+    cluster_barrier();                                            // every slice's sums and statistics are in place
+    for (int i = split * kAttnThreads + threadIdx.x; i < kGqa * hd; i += nsplit * kAttnThreads) {
+        const int h = i / hd, d = i - h * hd;
+        float m = -1e30f;
+        for (int r = 0; r < nsplit; r++) m = fmaxf(m, ld_dsmem_f32(dsmem_addr(stats + h, r)));
+        float num = 0.f, den = 0.f;
+        for (int r = 0; r < nsplit; r++) {
+            const float wgt = expf(ld_dsmem_f32(dsmem_addr(stats + h, r)) - m);   // an empty slice has max -1e30: weight 0
+            num += wgt * ld_dsmem_f32(dsmem_addr(accs + i, r));
+            den += wgt * ld_dsmem_f32(dsmem_addr(stats + kGqa + h, r));
+        }
+        P.out[((size_t)seq * P.n_head + (size_t)kvh * kGqa + h) * hd + d] = float_to_bf16_rne(num / den);
+    }
+    cluster_barrier();                                            // nobody reads this CTA's shared memory any more
 }
 
 // ---------------------------------------------------------------------------
@@ -500,8 +550,14 @@ static int attention_launch(AttnParams& P, int max_len, int batch, void* stream,
     const int gqa = P.n_head / P.n_head_kv;
     if (gqa != 1 && gqa != 2 && gqa != 4 && gqa != 8)
         return fail(S12_ERR_UNSUPPORTED, "%s: %d query heads per kv head (supported: 1, 2, 4, 8)", who, gqa);
-    P.score_stride = (max_len + 3) & ~3;
-    const size_t smem = ((size_t)gqa * P.score_stride + (size_t)kAttnWarps * gqa * P.head_dim) * sizeof(float);
+    // few (kv head, sequence) pairs: cut the positions into slices, one CTA each, merged inside a cluster
+    int nsplit = 1;
+    const long long pairs = (long long)P.n_head_kv * batch;
+    while (nsplit < 8 && pairs * nsplit * 2 <= sm_count() && max_len / (nsplit * 2) >= kAttnWarps) nsplit *= 2;
+    P.nsplit = nsplit;
+    const int per = (max_len + nsplit - 1) / nsplit;
+    P.score_stride = (per + 3) & ~3;
+    const size_t smem = ((size_t)gqa * P.score_stride + (size_t)kAttnWarps * gqa * P.head_dim + 2 * gqa) * sizeof(float);
     if (smem > 200 * 1024) return fail(S12_ERR_TOO_LARGE, "%s: seq_len %d needs more shared memory than one CTA has", who, max_len);
     typedef void (*Kern)(const AttnParams);
     static const Kern table[4][2] = {{attention_kernel<1, 1>, attention_kernel<1, 2>}, {attention_kernel<2, 1>, attention_kernel<2, 2>},
@@ -519,7 +575,7 @@ static int attention_launch(AttnParams& P, int max_len, int batch, void* stream,
             attr_set[dev][gi][ci] = true;
         }
     }
-    return launch(kern, dim3(P.n_head_kv, batch), dim3(kAttnThreads), smem, stream, who, P);
+    return launch_clustered_z(kern, dim3(P.n_head_kv, batch, nsplit), dim3(kAttnThreads), smem, stream, who, nsplit, P);
 }
 
 }  // namespace s12
