@@ -418,7 +418,7 @@ def run_ours(args):
                                   else "NCCL all_reduce between graph segments"),
                    "l2": "inputs larger than L2 (packed weights of one step: %.2f GB per GPU)" % (total_bytes / world / 1e9),
                    "launch": ("cuda graph" if graph is not None else "eager") + ("" if args.no_pdl else " + programmatic dependent launch"),
-                   "excluded": "norm/rope/attention/sampling kernels between the projections are not part of this path"},
+                   "excluded": "norm/rope/attention/argmax kernels between the projections are not timed here (the *_full workloads time the whole step)"},
         "compressed_GBps_per_gpu": round(per_gpu_gbs, 1),
         "roofline": roof,
         "e2e": {"value": round(B * args.steps / e2e_ms * 1e3, 2), "unit": "tok/s",

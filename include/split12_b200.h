@@ -334,6 +334,11 @@ int launch_attention_all_heads_batch(const float* q, const int8_t* kv_k, const i
 int s12_store_kv_batch(const float* k, const float* v, int8_t* kv_k, int8_t* kv_v, float* kv_scale_k,
                        float* kv_scale_v, const int* positions, int n_head_kv, int head_dim,
                        long long kv_stride, int batch_size, void* stream);
+/* launch_rope_batch followed by s12_store_kv_batch, as one launch. */
+int s12_rope_store_kv_batch(float* q, float* k, const float* v, int8_t* kv_k, int8_t* kv_v,
+                            float* kv_scale_k, float* kv_scale_v, const int* positions, int head_dim,
+                            int n_head, int n_head_kv, long long kv_stride, float theta, int batch_size,
+                            void* stream);
 
 /* --------------------------------------------------------------------------
  * Tensor parallelism: all-reduce after the row-parallel projections

@@ -71,6 +71,7 @@ SIGNATURES = {
     "launch_attention_all_heads": (_i, [_vp] * 6 + [_i, _i, _i, _i, _i, C.c_float, _vp]),
     "launch_attention_all_heads_batch": (_i, [_vp] * 7 + [_i, _i, _i, _i, C.c_float, _i, _i, _vp]),
     "s12_store_kv_batch": (_i, [_vp] * 7 + [_i, _i, C.c_longlong, _i, _vp]),
+    "s12_rope_store_kv_batch": (_i, [_vp] * 8 + [_i, _i, _i, C.c_longlong, C.c_float, _i, _vp]),
     "s12_comm_handle_bytes": (_i, []),
     "s12_comm_create": (_i, [_i, _i, C.c_longlong, C.POINTER(_vp), _vp]),
     "s12_comm_connect": (_i, [_vp, _vp]),

@@ -318,16 +318,23 @@ __device__ __forceinline__ void decode_row(const uint8_t* raw, int r, int sub, u
     const uint8_t* grow = raw + 2 * kRawBoxBytes + r * 128;
     const int sw = r & 7, sc = (sub & 1) * 4, gc = sub * 2;
 #pragma unroll
-    for (int c = 0; c < 4; c++) {                                // 16 columns per chunk
-        const uint4 s = *reinterpret_cast<const uint4*>(srow + (((sc + c) ^ sw) << 4));
-        const uint2 g = *reinterpret_cast<const uint2*>(grow + (((gc + (c >> 1)) ^ sw) << 4) + (c & 1) * 8);
-        uint32_t p[4];
-        decode8<kMode>(s.x, s.y, g.x, base2, p);
-        v[8 * c + 0] = prmt(p[0], p[1], 0x5410u); v[8 * c + 1] = prmt(p[2], p[3], 0x5410u);
-        v[8 * c + 2] = prmt(p[0], p[1], 0x7632u); v[8 * c + 3] = prmt(p[2], p[3], 0x7632u);
-        decode8<kMode>(s.z, s.w, g.y, base2, p);
-        v[8 * c + 4] = prmt(p[0], p[1], 0x5410u); v[8 * c + 5] = prmt(p[2], p[3], 0x5410u);
-        v[8 * c + 6] = prmt(p[0], p[1], 0x7632u); v[8 * c + 7] = prmt(p[2], p[3], 0x7632u);
+    for (int cc = 0; cc < 2; cc++) {                             // 32 columns: two 16-byte sm chunks, one 16-byte gr chunk
+        // 16-byte loads are served a quarter warp at a time, where the eight rows' swizzled chunks fall on
+        // different banks; an 8-byte load per 16 columns would pair rows r and r + 8 on the same banks
+        const uint4 gq = *reinterpret_cast<const uint4*>(grow + (((gc + cc) ^ sw) << 4));
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int c = 2 * cc + h;
+            const uint4 s = *reinterpret_cast<const uint4*>(srow + (((sc + c) ^ sw) << 4));
+            const uint32_t gx = h ? gq.z : gq.x, gy = h ? gq.w : gq.y;
+            uint32_t p[4];
+            decode8<kMode>(s.x, s.y, gx, base2, p);
+            v[8 * c + 0] = prmt(p[0], p[1], 0x5410u); v[8 * c + 1] = prmt(p[2], p[3], 0x5410u);
+            v[8 * c + 2] = prmt(p[0], p[1], 0x7632u); v[8 * c + 3] = prmt(p[2], p[3], 0x7632u);
+            decode8<kMode>(s.z, s.w, gy, base2, p);
+            v[8 * c + 4] = prmt(p[0], p[1], 0x5410u); v[8 * c + 5] = prmt(p[2], p[3], 0x5410u);
+            v[8 * c + 6] = prmt(p[0], p[1], 0x7632u); v[8 * c + 7] = prmt(p[2], p[3], 0x7632u);
+        }
     }
 }
 

@@ -129,10 +129,23 @@ silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, in
 {
     grid_launch_dependents();
     grid_dependency_wait();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;   // four elements per thread
     if (i >= total) return;
-    const float g = gate[i];
-    out[i] = float_to_bf16_rne(g / (1.0f + expf(-g)) * up[i]);
+    const bool vec = i + 3 < total && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+    if (vec) {
+        const float4 g = *reinterpret_cast<const float4*>(gate + i), u = *reinterpret_cast<const float4*>(up + i);
+        const uint32_t lo = (uint16_t)float_to_bf16_rne(g.x / (1.0f + expf(-g.x)) * u.x) |
+                            ((uint32_t)(uint16_t)float_to_bf16_rne(g.y / (1.0f + expf(-g.y)) * u.y) << 16);
+        const uint32_t hi = (uint16_t)float_to_bf16_rne(g.z / (1.0f + expf(-g.z)) * u.z) |
+                            ((uint32_t)(uint16_t)float_to_bf16_rne(g.w / (1.0f + expf(-g.w)) * u.w) << 16);
+        *reinterpret_cast<uint2*>(out + i) = make_uint2(lo, hi);
+        return;
+    }
+    for (long long j = i; j < total && j < i + 4; j++) {
+        const float g = gate[j];
+        out[j] = float_to_bf16_rne(g / (1.0f + expf(-g)) * up[j]);
+    }
 }
 __global__ void __launch_bounds__(256)
 add_kernel(float* __restrict__ y, const float* __restrict__ x, long long total)
@@ -298,6 +311,12 @@ attention_kernel(const __grid_constant__ AttnParams P)
     float* scores = att_smem;
     float* accs = att_smem + (size_t)kGqa * ss;
     float* stats = accs + (size_t)kAttnWarps * kGqa * hd;        // [0][h]: slice maximum, [1][h]: slice sum of exp
+    float* sk_s = stats + 2 * kGqa;                               // this slice's key and value scales (strided in memory)
+    float* sv_s = sk_s + ss;
+    for (int i = threadIdx.x; i < t_hi - t_lo; i += kAttnThreads) {
+        sk_s[i] = sk[(size_t)(t_lo + i) * P.n_head_kv];
+        sv_s[i] = sv[(size_t)(t_lo + i) * P.n_head_kv];
+    }
 
     // a lane owns elements [128*c + 4*lane, +4) of the head, c < kChunks
     bool live[kChunks];
@@ -310,6 +329,7 @@ attention_kernel(const __grid_constant__ AttnParams P)
 #pragma unroll
             for (int e = 0; e < 4; e++) qv[h][c][e] = live[c] ? q[(size_t)h * hd + c * 128 + lane * 4 + e] : 0.f;
     }
+    __syncthreads();
     // ---- scores of this slice (indexed from t_lo in shared memory)
     for (int t0 = t_lo + warp; t0 < t_hi; t0 += kAttnFlight * kAttnWarps) {
         int w[kAttnFlight][kChunks];
@@ -343,7 +363,7 @@ attention_kernel(const __grid_constant__ AttnParams P)
                 float mine = dot[0];
 #pragma unroll
                 for (int h = 1; h < kGqa; h++) mine = lane == h ? dot[h] : mine;
-                scores[lane * ss + (t - t_lo)] = mine * sk[(size_t)t * P.n_head_kv] * P.scale;
+                scores[lane * ss + (t - t_lo)] = mine * sk_s[t - t_lo] * P.scale;
             }
         }
     }
@@ -358,7 +378,7 @@ attention_kernel(const __grid_constant__ AttnParams P)
         float sum = 0.f;
         for (int i = lane; i < n_loc; i += 32) {
             const float e = expf(scores[h * ss + i] - m);
-            scores[h * ss + i] = e * sv[(size_t)(t_lo + i) * P.n_head_kv];
+            scores[h * ss + i] = e * sv_s[i];
             sum += e;
         }
 #pragma unroll
@@ -557,7 +577,7 @@ static int attention_launch(AttnParams& P, int max_len, int batch, void* stream,
     P.nsplit = nsplit;
     const int per = (max_len + nsplit - 1) / nsplit;
     P.score_stride = (per + 3) & ~3;
-    const size_t smem = ((size_t)gqa * P.score_stride + (size_t)kAttnWarps * gqa * P.head_dim + 2 * gqa) * sizeof(float);
+    const size_t smem = ((size_t)(gqa + 2) * P.score_stride + (size_t)kAttnWarps * gqa * P.head_dim + 2 * gqa) * sizeof(float);
     if (smem > 200 * 1024) return fail(S12_ERR_TOO_LARGE, "%s: seq_len %d needs more shared memory than one CTA has", who, max_len);
     typedef void (*Kern)(const AttnParams);
     static const Kern table[4][2] = {{attention_kernel<1, 1>, attention_kernel<1, 2>}, {attention_kernel<2, 1>, attention_kernel<2, 2>},
@@ -618,7 +638,7 @@ int launch_silu_mul_bf16_batch(const float* gate, const float* up, int16_t* out,
 {
     if (!gate || !up || !out || n < 1 || batch_size < 1) return fail(S12_ERR_BAD_ARG, "launch_silu_mul_bf16_batch: bad argument");
     const long long total = (long long)n * batch_size;
-    return launch(silu_mul_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, "launch_silu_mul_bf16_batch",
+    return launch(silu_mul_kernel, dim3((unsigned)((total + 1023) / 1024)), dim3(256), 0, stream, "launch_silu_mul_bf16_batch",
                   gate, up, out, total);
 }
 int launch_add_batch(float* y, const float* x, int n, int batch_size, void* stream)
@@ -659,6 +679,19 @@ int s12_store_kv_batch(const float* k, const float* v, int8_t* kv_k, int8_t* kv_
     P.positions = positions; P.head_dim = head_dim; P.n_head = 0; P.n_head_kv = n_head_kv;
     P.k_stride = n_head_kv * head_dim; P.kv_stride = kv_stride; P.rope = 0; P.store = 1;
     return rope_kv_launch(P, 10000.0f, batch_size, stream, "store_kv_batch");
+}
+// launch_rope_batch and s12_store_kv_batch as one launch.
+int s12_rope_store_kv_batch(float* q, float* k, const float* v, int8_t* kv_k, int8_t* kv_v, float* kv_scale_k, float* kv_scale_v,
+                            const int* positions, int head_dim, int n_head, int n_head_kv, long long kv_stride, float theta,
+                            int batch_size, void* stream)
+{
+    if (!q || !k || !v || !kv_k || !kv_v || !kv_scale_k || !kv_scale_v || !positions)
+        return fail(S12_ERR_BAD_ARG, "s12_rope_store_kv_batch: null argument");
+    RopeKvParams P = {};
+    P.q = q; P.k = k; P.v = v; P.kv_k = kv_k; P.kv_v = kv_v; P.sc_k = kv_scale_k; P.sc_v = kv_scale_v;
+    P.positions = positions; P.head_dim = head_dim; P.n_head = n_head; P.n_head_kv = n_head_kv;
+    P.q_stride = n_head * head_dim; P.k_stride = n_head_kv * head_dim; P.kv_stride = kv_stride; P.rope = 1; P.store = 1;
+    return rope_kv_launch(P, theta, batch_size, stream, "s12_rope_store_kv_batch");
 }
 int launch_store_kv_batch(const float* k, const float* v, int8_t* kv_k, int8_t* kv_v, float* kv_scale_k, float* kv_scale_v,
                           const int* positions, int kv_dim, int max_seq, int n_head_kv, int head_dim, int batch_size, void* stream)

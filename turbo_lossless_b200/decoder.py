@@ -99,9 +99,8 @@ class Decoder:
                     self._proj([w], self.bf16_a, [o])
             else:
                 self._proj([L["wq"], L["wk"], L["wv"]], self.bf16_a, [self.q_buf, self.k_buf, self.v_buf])
-            e.rope_batch(self.q_buf, self.k_buf, self.positions, hd, c.n_head, c.n_head_kv, c.rope_theta, B)
-            e.store_kv_batch(self.k_buf, self.v_buf, self.kv_k[li], self.kv_v[li], self.sc_k[li], self.sc_v[li],
-                             self.positions, c.n_head_kv, hd, B, kv_stride=self.kv_stride)
+            e.rope_store_kv_batch(self.q_buf, self.k_buf, self.v_buf, self.kv_k[li], self.kv_v[li], self.sc_k[li], self.sc_v[li],
+                                  self.positions, hd, c.n_head, c.n_head_kv, self.kv_stride, c.rope_theta, B)
             e.attention_all_heads_batch(self.q_buf, self.kv_k[li], self.kv_v[li], self.sc_k[li], self.sc_v[li], self.bf16_a,
                                         self.positions, c.n_head, c.n_head_kv, hd, attn_len, scale, B, self.kv_stride)
             self._proj([L["wo"]], self.bf16_a, [res])
@@ -119,5 +118,5 @@ class Decoder:
         e.argmax(self.logits, self.next_tokens)
 
     def launches_per_step(self) -> int:
-        per_layer = 10 if not (1 < self.B <= 16) else 13
+        per_layer = 9 if not (1 < self.B <= 16) else 12
         return 1 + 1 + per_layer * len(self.layers) + 2

@@ -359,6 +359,12 @@ class Split12Engine:
                                               _ptr(positions), n_head_kv, head_dim, kv_stride, batch, _stream(stream)),
                   "s12_store_kv_batch")
 
+    def rope_store_kv_batch(self, q, k, v, kv_k, kv_v, scale_k, scale_v, positions, head_dim: int, n_head: int,
+                            n_head_kv: int, kv_stride: int, theta: float, batch: int, stream=None) -> None:
+        check(self.lib.s12_rope_store_kv_batch(_ptr(q), _ptr(k), _ptr(v), _ptr(kv_k), _ptr(kv_v), _ptr(scale_k), _ptr(scale_v),
+                                               _ptr(positions), head_dim, n_head, n_head_kv, kv_stride, theta, batch,
+                                               _stream(stream)), "s12_rope_store_kv_batch")
+
     def attention_all_heads(self, q, kv_k, kv_v, scale_k, scale_v, out_bf16, n_head: int, n_head_kv: int, head_dim: int,
                             seq_len: int, max_seq: int, scale: float, stream=None) -> None:
         check(self.lib.launch_attention_all_heads(_ptr(q), _ptr(kv_k), _ptr(kv_v), _ptr(scale_k), _ptr(scale_v),
