@@ -80,6 +80,7 @@ struct StreamParams {
     int tpr;                // tiles per row block = ceil(K / (Q*1024))
     int depth;              // ring stages
     int total_blocks;
+    int slots;              // > 0: the grid is 2 x slots CTAs and blocks are dealt per slot (see the kernel)
     unsigned int* status;
     DecodeMul mul;          // {128, 8, 1<<24}: see decode8_fma
     // Tensor-parallel form (row-parallel shard, one tensor): the epilogue pushes every finished row to
@@ -157,9 +158,22 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
     // there the dependents are released after the wait.
     if (P.tp_world == 0) grid_launch_dependents();
 
-    // this CTA's contiguous range of row blocks
-    const int b0 = (int)(((long long)blockIdx.x * P.total_blocks) / gridDim.x);
-    const int b1 = (int)(((long long)(blockIdx.x + 1) * P.total_blocks) / gridDim.x);
+    // This CTA's contiguous range of row blocks.  With two CTAs per SM the blocks are first dealt to the
+    // SMs (slot = blockIdx % slots; CTAs i and i + slots normally share an SM) and a slot's share is then
+    // halved between its two CTAs, so that the load is even per SM: dealing to 2 x slots CTAs directly
+    // leaves SMs with 3+3 and others with 4+4 blocks on a 1024-block tensor.
+    int b0, b1;
+    if (P.slots > 0) {
+        const int slot = (int)blockIdx.x % P.slots, half = (int)blockIdx.x / P.slots;
+        const int s0 = (int)(((long long)slot * P.total_blocks) / P.slots);
+        const int s1 = (int)(((long long)(slot + 1) * P.total_blocks) / P.slots);
+        const int mid = s0 + (s1 - s0 + (slot & 1)) / 2;          // odd shares alternate which half gets the extra block
+        b0 = half ? mid : s0;
+        b1 = half ? s1 : mid;
+    } else {
+        b0 = (int)(((long long)blockIdx.x * P.total_blocks) / gridDim.x);
+        b1 = (int)(((long long)(blockIdx.x + 1) * P.total_blocks) / gridDim.x);
+    }
     const int nblocks = b1 - b0;
     const int ntiles = nblocks * P.tpr;
     const int K = P.K, R = P.R, Q = P.Q;
@@ -509,6 +523,7 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     const int slots = sms * ctas;
     const int grid = blocks < slots ? blocks : slots;
     if (comm && grid > kCommMaxCtas) return 0;
+    P.slots = (ctas == 2 && grid == 2 * sms && blocks >= 2 * grid) ? sms : 0;
     *rc_out = launch(kern, dim3(grid), dim3(stream_threads(groups)), smem, stream, who, P);
     return *rc_out == S12_OK ? 1 : -1;
 }
