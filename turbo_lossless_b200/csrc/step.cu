@@ -263,6 +263,7 @@ struct AttnParams {
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
 constexpr int kAttnFlight = 8;           // positions in flight per warp
+// exponentials of softmax weights use the fast intrinsic: arguments are <= 0 and the result feeds a bf16 output
 
 __device__ __forceinline__ void unpack_s8x4(int w, float (&f)[4])
 {
@@ -377,7 +378,7 @@ attention_kernel(const __grid_constant__ AttnParams P)
         for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
         float sum = 0.f;
         for (int i = lane; i < n_loc; i += 32) {
-            const float e = expf(scores[h * ss + i] - m);
+            const float e = __expf(scores[h * ss + i] - m);
             scores[h * ss + i] = e * sv_s[i];
             sum += e;
         }
@@ -452,7 +453,7 @@ attention_kernel(const __grid_constant__ AttnParams P)
         for (int r = 0; r < nsplit; r++) m = fmaxf(m, ld_dsmem_f32(dsmem_addr(stats + h, r)));
         float num = 0.f, den = 0.f;
         for (int r = 0; r < nsplit; r++) {
-            const float wgt = expf(ld_dsmem_f32(dsmem_addr(stats + h, r)) - m);   // an empty slice has max -1e30: weight 0
+            const float wgt = __expf(ld_dsmem_f32(dsmem_addr(stats + h, r)) - m);   // an empty slice has max -1e30: weight 0
             num += wgt * ld_dsmem_f32(dsmem_addr(accs + i, r));
             den += wgt * ld_dsmem_f32(dsmem_addr(stats + kGqa + h, r));
         }
