@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_util import assert_close, dev
+from gpu_util import REL_TOL, assert_close, dev
 
 pytestmark = pytest.mark.gpu
 
@@ -100,3 +100,29 @@ def test_multi_tensor_launch_qkv(eng, O, B):
         assert_close(o[:, :p.M], O.gemm_exact(w, x), what=f"M={p.M}")
         assert torch.isnan(o[:, p.M:]).all()
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("knobs", [{"S12_GEMM_CLUSTER": "0", "S12_GEMM_SPLIT": "0"},      # stream-K with owner hand-over
+                                   {"S12_GEMM_CLUSTER": "0", "S12_GEMM_SPLIT": "1"},      # whole tiles
+                                   {"S12_GEMM_CLUSTER": "0", "S12_GEMM_SPLIT": "3"},      # fixed parts, hand-over through the workspace
+                                   {"S12_GEMM_CLUSTER": "2"}, {"S12_GEMM_CLUSTER": "5"}, {"S12_GEMM_CLUSTER": "8"},
+                                   {}])                                                    # the library's own choice
+@pytest.mark.parametrize("M,K,B", [(1000, 4096, 256), (3000, 2048, 100), (20000, 1024, 48)])
+def test_every_schedule_gives_the_oracle_result(eng, O, monkeypatch, knobs, M, K, B):
+    """The tensor-core GEMM's schedules (stream-K, whole tiles, fixed K parts, clusters of 2..8 CTAs per tile) are
+    selected by a cost model; the tuning knobs force each of them here.  Two runs of a schedule are bit-identical."""
+    for k, v in knobs.items():
+        monkeypatch.setenv(k, v)
+    w, p, x = _case(O, M, K, B, M + B, frac=2e-3)
+    cw = _cw(p)
+    xd = torch.from_numpy(x.view(np.int16)).cuda()
+    outs = []
+    for _ in range(2):
+        out = torch.full((B, M), float("nan"), device="cuda")
+        eng.gemm(cw, xd, out, K, M, B)
+        torch.cuda.synchronize()
+        outs.append(out.cpu().numpy())
+    assert eng.device_status() == 0
+    ref = O.gemm_exact(w, x)
+    assert np.abs(outs[0] - ref).max() <= REL_TOL * np.abs(ref).max()
+    np.testing.assert_array_equal(outs[0], outs[1])
