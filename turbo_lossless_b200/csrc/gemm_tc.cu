@@ -9,7 +9,8 @@
 //                loads (two 128 B x 128-row sm boxes, one 128 B x 128-row gr box,
 //                128-byte swizzle) into a two-stage ring; weights come from HBM
 //   warp 2       activation producer: TMA loads of the activation tile
-//                (BN sequences x 64 k, 128-byte swizzle) into its own ring
+//                (BN sequences x 64 k, 128-byte swizzle), four stages; stage s
+//                pairs with A stage s and shares its barriers
 //   warp 1       owns tensor memory (alloc/dealloc) and issues the MMAs from
 //                one thread: per 64-column block 4 tcgen05.mma (M=128, N=BN,
 //                K=16, bf16 x bf16 -> fp32), A operand read from tensor memory
@@ -19,16 +20,19 @@
 //                brings one) and writes them with tcgen05.st into A stage g
 //   warps 20-23  epilogue: tcgen05.ld of the finished accumulators (double
 //                buffered in TMEM when 2*BN <= 384 columns), coalesced fp32
-//                stores (32 consecutive m per store)
-//   warp 3       idle
+//                stores (32 consecutive m per store); with a single-buffered
+//                accumulator (BN = 256) the decode warps drain with them
+//   warp 3       warms the tensor-map descriptors, then idle
 //
-// Work is split stream-K style: the (M tiles x N tiles x 256-column blocks) iteration
-// space is cut into equal contiguous ranges, one per CTA, so a 4096-row
-// projection (32 tiles) still occupies all 148 SMs.  A CTA that covers only
-// part of a tile's K range and does not hold the tile's first iteration writes
-// its partial accumulator to a workspace; the CTA that does hold it adds those
-// partials to its own while it drains, in CTA order, so the output is
-// deterministic.  Shapes with few tiles use thread-block clusters instead (below).
+// Three schedules, chosen on the host (choose_schedule).  Stream-K: the
+// (M tiles x N tiles x 256-column blocks) iteration space is cut into equal
+// contiguous ranges, one per CTA; a CTA that covers only part of a tile's K
+// range and does not hold the tile's first iteration writes its partial
+// accumulator to a workspace, and the CTA that does hold it adds those partials
+// to its own while it drains, in CTA order.  Whole tiles, one per CTA, when the
+// tiles fit one round.  Few tiles (a 4096-row projection has 32): every tile is
+// cut into s K parts that run as a thread-block cluster and add up over
+// distributed shared memory (cluster_reduce).  All three are deterministic.
 //
 // Escapes: with the CSR list the decoded weights are exact inside the MMA;
 // without it they keep the reference's "wrong" value (exponent base_exp), which
@@ -172,20 +176,12 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols)
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, fp32 accumulate
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// same with the A operand in tensor memory (lane = row, one 32-bit column = two consecutive k)
+// D[tmem] (+)= A[tmem] * B[smem desc], bf16 inputs, fp32 accumulate; A in tensor memory: lane = row, one 32-bit
+// column = two consecutive k
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile("{\n\t.reg .pred p;\n\t"
