@@ -4,11 +4,14 @@
 // matrix sizes of a decode step, by how quickly every SM gets enough bytes in
 // flight and keeps them in flight until the last byte.  Design:
 //
-//   * One persistent CTA per SM.  A producer warp streams the packed weights
-//     into a ring of shared-memory stages with 1-D bulk copies
-//     (cp.async.bulk, completion counted on an mbarrier), so up to
-//     depth x 24 KB per SM are in flight without holding registers, and the
-//     stream does not pause between row blocks.
+//   * Persistent CTAs, two per SM by default (template kGroups = 1: one group of
+//     eight consumer warps, 11 warps in all; kGroups = 2: one CTA per SM with
+//     two groups working on alternate tiles).  A producer warp streams the
+//     packed weights into a ring of shared-memory stages with 1-D bulk copies
+//     (cp.async.bulk, completion counted on an mbarrier), so depth x 24 KB per
+//     CTA are in flight without holding registers, and the stream does not
+//     pause between row blocks.  Row blocks are dealt per SM and halved between
+//     its two CTAs.
 //   * A stage holds one tile = 16 segments of 1024 columns (1 KB of sm and
 //     512 B of gr each).  The 16 segments are the 16 rows of the A operand of
 //     mma.sync.m16n8k16; which matrix row/column range a segment covers is a
@@ -24,10 +27,10 @@
 //     as large as K allows.  Small R also gives many small work units
 //     (a 4096-row matrix becomes 1024 units for 148 SMs) with no cross-CTA
 //     reduction.
-//   * Sixteen consumer warps in two groups (alternate tiles); inside a group each
-//     warp takes 128 columns of every segment of the tile:
-//     16-byte shared loads, decode8 in registers (about 2 integer instructions
-//     per weight), tensor-core multiply-accumulate.
+//   * Inside a consumer group each warp takes 128 columns of every segment of
+//     the tile: 16-byte shared loads, decode8_fma in registers (about 2 integer
+//     instructions per weight, the shifts issued as multiplies so that they run
+//     on the FMA pipe next to the ALU pipe), tensor-core multiply-accumulate.
 //   * Two epilogue warps own the per-row-block tail, 16 rows at a time: they compute the escape
 //     correction sum_p (correct_p - wrong_p) * x[col_p] (second pass of the
 //     reference, nvidia_kernels.cu:271-290) from global memory while the
@@ -36,7 +39,10 @@
 //   * Under programmatic dependent launch the producer starts filling the ring
 //     immediately (weights are never written); only the consumers' staging of
 //     the activation vector and the epilogue's stores wait for the predecessor.
-//   * All mbarrier waits are bounded (common.cuh).
+//   * Tensor-parallel form (one row-parallel tensor): the epilogue pushes every
+//     finished row into all ranks' receive areas and the CTA adds the ranks'
+//     partials of its own rows (comm.cuh).
+//   * All waits are bounded (common.cuh).
 #include "comm.cuh"
 #include <cstdlib>
 
