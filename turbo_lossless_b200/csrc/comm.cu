@@ -21,6 +21,7 @@
 //
 // Plain peer stores and loads only: no multimem, no TMA.
 #include "comm.cuh"
+#include <algorithm>
 #include <mutex>
 #include <vector>
 
@@ -70,6 +71,53 @@ allreduce_kernel(const __grid_constant__ AllReduceParams P)
     if (threadIdx.x == 0) comm_retire(R, token, gridDim.x);
 }
 
+// Small vectors (a B = 1 hidden state is 16 KB): latency is everything, so value and arrival token travel
+// in ONE 8-byte word.  A rank stores {bits, token} of each of its elements into every rank's area and then
+// polls, element by element, the words the other ranks stored for it: no fence, no separate flag, no
+// CTA-wide step (8-byte scalar accesses are single-copy atomic, so a word is either old or whole).  Twice
+// the bytes on the wire, about half the latency.  Parity and the call counter work as above.
+__global__ void __launch_bounds__(256)
+allreduce_ll_kernel(const __grid_constant__ AllReduceParams P)
+{
+    const CommRank& R = P.r[blockIdx.y];
+    const float* in = P.in[blockIdx.y];
+    float* out = P.out[blockIdx.y];
+    const int world = P.world, me = R.rank;
+    if (P.early_trigger) grid_launch_dependents();
+    grid_dependency_wait();
+    int parity;
+    const unsigned int token = comm_begin(R, parity);
+    const int first = blockIdx.x * blockDim.x + threadIdx.x, step = gridDim.x * blockDim.x;
+    for (int i = first; i < P.n; i += step) {
+        const unsigned long long word = ((unsigned long long)token << 32) | (unsigned long long)__float_as_uint(in[i]);
+#pragma unroll 1
+        for (int p = 0; p < world; p++)
+            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(R.ll[p] + ((size_t)parity * world + me) * kCommLLMax + i), "l"(word) : "memory");
+    }
+    if (!P.early_trigger) grid_launch_dependents();
+    const unsigned long long* mine = R.ll[me] + (size_t)parity * world * kCommLLMax;
+    unsigned long long t0 = 0;
+    bool gave_up = false;
+    for (int i = first; i < P.n; i += step) {
+        float acc = 0.f;
+#pragma unroll 1
+        for (int p = 0; p < world; p++) {
+            unsigned long long word;
+            for (;;) {
+                asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(mine + (size_t)p * kCommLLMax + i) : "memory");
+                if ((unsigned int)(word >> 32) == token || gave_up) break;
+                const unsigned long long now = global_time_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > kPeerWaitLimitNs) { atomicOr(R.status, 0x8000u); gave_up = true; }   // the peer never arrived
+            }
+            acc += __uint_as_float((unsigned int)word);
+        }
+        out[i] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) comm_retire(R, token, gridDim.x);
+}
+
 }  // namespace s12
 
 // ----------------------------------------------------------------------------
@@ -79,7 +127,7 @@ struct S12Comm {
     int rank = 0, world = 1, device = 0;
     int capacity = 0;                         // floats per receive row
     char* base = nullptr;                     // local allocation: recv area, then flag area
-    size_t recv_bytes = 0, flag_bytes = 0;
+    size_t recv_bytes = 0, flag_bytes = 0, ll_bytes = 0;
     char* peer_base[s12::kCommMaxWorld] = {};  // every rank's allocation as mapped in this process
     bool opened[s12::kCommMaxWorld] = {};      // mapped through an IPC handle (must be closed)
     unsigned int* calls = nullptr;             // [0] calls completed, [1] CTAs done in the running call
@@ -104,8 +152,11 @@ int s12_comm_create(int rank, int world, long long max_floats, S12Comm** out, vo
     c->recv_bytes = (size_t)2 * world * c->capacity * sizeof(float);
     c->recv_bytes = (c->recv_bytes + 255) & ~(size_t)255;
     c->flag_bytes = (size_t)2 * kCommMaxCtas * world * sizeof(unsigned int);
-    if (!rc) rc = check_cuda(cudaMalloc(&c->base, c->recv_bytes + c->flag_bytes), who);
-    if (!rc) rc = check_cuda(cudaMemset(c->base, 0, c->recv_bytes + c->flag_bytes), who);
+    c->flag_bytes = (c->flag_bytes + 255) & ~(size_t)255;
+    c->ll_bytes = (size_t)2 * world * kCommLLMax * sizeof(unsigned long long);
+    const size_t total = c->recv_bytes + c->flag_bytes + c->ll_bytes;
+    if (!rc) rc = check_cuda(cudaMalloc(&c->base, total), who);
+    if (!rc) rc = check_cuda(cudaMemset(c->base, 0, total), who);
     if (!rc) rc = check_cuda(cudaMalloc(&c->calls, 2 * sizeof(unsigned int)), who);
     if (!rc) rc = check_cuda(cudaMemset(c->calls, 0, 2 * sizeof(unsigned int)), who);
     if (!rc && handle_out) {
@@ -161,6 +212,7 @@ static int fill_rank(const S12Comm* c, s12::CommRank& R)
     for (int p = 0; p < c->world; p++) {
         R.recv[p] = reinterpret_cast<float*>(c->peer_base[p]);
         R.flags[p] = reinterpret_cast<unsigned int*>(c->peer_base[p] + c->recv_bytes);
+        R.ll[p] = reinterpret_cast<unsigned long long*>(c->peer_base[p] + c->recv_bytes + c->flag_bytes);
     }
     R.calls = c->calls;
     R.status = s12::device_status_word();
@@ -192,6 +244,12 @@ int s12_allreduce_f32_async(S12Comm* c, const void* in, void* out, int n, void* 
     P.world = c->world; P.capacity = c->capacity; P.n = n;
     const char* e = getenv("S12_COMM_EARLY");                     // tuning knob, default on
     P.early_trigger = e ? atoi(e) : 1;
+    const char* ll = getenv("S12_COMM_LL");                       // tuning knob, default on
+    if (n <= kCommLLMax && (!ll || atoi(ll))) {
+        int ctas = (n + 1023) / 1024;
+        ctas = ctas > 16 ? 16 : ctas;
+        return launch(allreduce_ll_kernel, dim3(ctas, 1), dim3(256), 0, stream, who, P);
+    }
     return launch(allreduce_kernel, dim3(comm_ctas(n), 1), dim3(kCommThreads), 0, stream, who, P);
 }
 
@@ -211,15 +269,19 @@ int s12_allreduce_f32_emulated_async(S12Comm* const* comms, int world, const voi
         P.in[r] = (const float*)ins[r]; P.out[r] = (float*)outs[r];
     }
     P.world = world; P.capacity = comms[0]->capacity; P.n = n;
-    const int ctas = comm_ctas(n);
+    const char* ll = getenv("S12_COMM_LL");
+    const bool small = n <= kCommLLMax && (!ll || atoi(ll));
+    const int ctas = small ? std::min(16, (n + 1023) / 1024) : comm_ctas(n);
+    const int threads = small ? 256 : kCommThreads;
+    const void* kern = small ? (const void*)allreduce_ll_kernel : (const void*)allreduce_kernel;
     int per_sm = 0;
-    int rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_kernel, kCommThreads, 0), who);
+    int rc = check_cuda(small ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_ll_kernel, threads, 0)
+                              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_kernel, threads, 0), who);
     if (rc) return rc;
     if ((long long)ctas * world > (long long)per_sm * sm_count())
         return fail(S12_ERR_TOO_LARGE, "%s: %d x %d CTAs cannot be resident together", who, ctas, world);
     void* args[1] = {&P};
-    return check_cuda(cudaLaunchCooperativeKernel((const void*)allreduce_kernel, dim3(ctas, world), dim3(kCommThreads), args, 0,
-                                                  (cudaStream_t)stream), who);
+    return check_cuda(cudaLaunchCooperativeKernel(kern, dim3(ctas, world), dim3(threads), args, 0, (cudaStream_t)stream), who);
 }
 
 int s12_comm_destroy(S12Comm* c)

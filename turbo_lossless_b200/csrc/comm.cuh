@@ -23,11 +23,13 @@ namespace s12 {
 constexpr int kCommMaxWorld = 8;
 constexpr int kCommMaxCtas = 512;         // flag slots per parity: CTAs of the largest launch that signals
 constexpr int kCommThreads = 512;
+constexpr int kCommLLMax = 16384;          // floats: vectors up to this size take the small-message form
 constexpr int kCommMinSlice = 2048;          // floats per CTA before another CTA is added
 
 struct CommRank {
     float* recv[kCommMaxWorld];              // every rank's receive area (index = owner rank), as mapped here
     unsigned int* flags[kCommMaxWorld];      // every rank's flag area
+    unsigned long long* ll[kCommMaxWorld];   // every rank's small-message area: 8-byte words {value bits, token}
     unsigned int* calls;                     // local: [0] collective calls completed, [1] CTAs of the running call that are done
     unsigned int* status;                    // local status word (bit 0x8000: a wait gave up)
     int rank;
