@@ -244,6 +244,39 @@ int s12_host_build_escape_table(const int32_t* row_off, const int32_t* cols,
                                 int32_t* row_base, uint8_t* counts, int16_t* vals,
                                 int32_t* nonempty_rows);
 
+/* =========================================================================
+ * 3b. Load-time path on the device
+ * ========================================================================= */
+
+/* The same two structures built by kernels from DEVICE copies of the CSR list
+ * (one warp per row ranks the row's escapes by (col mod 256, position); one
+ * block compacts the rows that have escapes).  esc_row_base / esc_vals /
+ * esc_counts (optional, M*256 bytes) and nonempty_rows (M ints) / num_nonempty
+ * (one int, device) are device buffers of the caller; either group may be null.
+ * Asynchronous.  Replaces engine/model.cpp:86-156 without the host passes. */
+int s12_build_escape_table_async(const void* row_off, const void* cols, const void* correct, int M,
+                                 void* esc_row_base, void* esc_counts, void* esc_vals,
+                                 void* nonempty_rows, void* num_nonempty, void* stream);
+
+/* Reads <dir>/<prefix>.dims ("M K num_patches [base_exp]"; base_exp = 0 when
+ * the field is absent, engine/model.cpp:34-43). */
+int s12_tensor_dims(const char* dir, const char* prefix, int* M, int* K,
+                    int64_t* num_patches, int* base_exp);
+
+/* Loads one packed tensor written by engine/convert_model.py:127-134 into
+ * device buffers of the caller sized from s12_tensor_dims (sm M*K, gr M*K/2,
+ * row_off M+1 ints, cols/correct/wrong num_patches entries) and builds the
+ * escape table and non-empty row list on the device (null = skip).  Files go
+ * through a pinned double buffer, so disk reads overlap the copies.  Missing or
+ * empty CSR files mean "no escapes" (engine/model.cpp:45-66); missing sm/gr or
+ * sizes that contradict the dims are errors.  Synchronises `stream` before
+ * returning.  Returns the number of escapes loaded or a negative S12_ERR_*;
+ * *num_nonempty (host, may be null) receives the length of the row list.
+ * Replaces load_compressed, engine/model.cpp:32-163. */
+int64_t s12_load_tensor(const char* dir, const char* prefix, void* sm, void* gr, void* row_off, void* cols,
+                          void* correct, void* wrong, void* esc_row_base, void* esc_counts, void* esc_vals,
+                          void* nonempty_rows, int* num_nonempty, void* stream);
+
 /* Tensor-parallel shards of a packed tensor (new: the reference is single
  * GPU).  Outputs are caller-allocated for the worst case (all escapes of the
  * source).  Return the shard's escape count, or a negative S12_ERR_*.

@@ -126,3 +126,23 @@ def test_loader_reads_the_on_disk_format(tmp_path, O):
     os.remove(os.path.join(d, "layer.0.wq.gr.bin"))
     with pytest.raises(FileNotFoundError):
         CompressedWeight.from_dir(d, "layer.0.wq", device="cpu")
+
+
+def test_model_config_and_context_length(tmp_path):
+    """config.bin layout and the context-length rule of engine/model.cpp:181-258."""
+    import struct
+    from turbo_lossless_b200.loader import context_length, read_config
+    with open(tmp_path / "config.bin", "wb") as f:
+        f.write(struct.pack("<7i2f", 32000, 4096, 32, 8, 32, 14336, 32768, 1e6, 1e-5))
+    cfg = read_config(str(tmp_path))
+    assert (cfg["n_vocab"], cfg["n_embd"], cfg["n_head"], cfg["n_head_kv"], cfg["n_layer"], cfg["n_ff"], cfg["n_ctx"]) == \
+        (32000, 4096, 32, 8, 32, 14336, 32768)
+    assert cfg["rope_theta"] == 1e6 and abs(cfg["rms_norm_eps"] - 1e-5) < 1e-12
+    per_token = 32 * 8 * (128 * 2 + 8)
+    assert context_length(cfg, 1, 100 << 30) == 8192                       # capped by the default
+    assert context_length(cfg, 1, (512 << 20) + 1000 * per_token) == 1000  # capped by free memory less 512 MB
+    assert context_length(cfg, 4, (512 << 20) + 4000 * per_token) == 1000  # every sequence has its own cache
+    assert context_length(cfg, 1, 100 * per_token) == 128                  # never below 128
+    assert context_length(cfg, 1, 1 << 40, env="300") == 300 and context_length(cfg, 1, 1 << 40, env="5") == 128
+    with pytest.raises(FileNotFoundError):
+        read_config(str(tmp_path / "missing"))

@@ -9,5 +9,6 @@ sites; all arithmetic of the path runs in the CUDA library.
 from .capi import S12Error, S12Tensor, load  # noqa: F401
 from .engine import CompressedWeight, Split12Engine, TPComm  # noqa: F401
 from .decoder import Decoder, DecoderConfig  # noqa: F401
+from .loader import load_model, read_config  # noqa: F401
 
-__all__ = ["S12Error", "S12Tensor", "load", "CompressedWeight", "Split12Engine", "TPComm", "Decoder", "DecoderConfig"]
+__all__ = ["S12Error", "S12Tensor", "load", "CompressedWeight", "Split12Engine", "TPComm", "Decoder", "DecoderConfig", "load_model", "read_config"]

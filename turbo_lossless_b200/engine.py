@@ -158,10 +158,62 @@ class CompressedWeight:
                                           correct.data_ptr(), wrong.data_ptr(), st), "s12_pack_fill_async")
             out.row_offsets, out.patch_cols, out.patch_correct, out.patch_wrong = row_off, cols, correct, wrong
             if escape_table:
-                host = cls.from_host(M, K, base_exp, sm.cpu().numpy(), gr.cpu().numpy(), row_off.cpu().numpy(),
-                                     cols.cpu().numpy(), correct.cpu().numpy(), wrong.cpu().numpy(), device=dev)
-                return host
+                out.build_escape_table_on_device()
         return out
+
+    def build_escape_table_on_device(self, escape_counts: bool = False, stream=None) -> None:
+        """Escape table of the batch4/8 path and the non-empty row list, built by kernels from the CSR list that
+        is already on the device (the load-time passes of engine/model.cpp:86-156 without the host)."""
+        if self.num_patches <= 0 or self.row_offsets is None:
+            return
+        lib = capi.load()
+        dev = self.split_sm.device
+        self.escape_row_base = torch.empty(self.M, dtype=torch.int32, device=dev)
+        self.escape_vals = torch.empty(self.num_patches, dtype=torch.int16, device=dev)
+        self.escape_counts = torch.empty(self.M * 256, dtype=torch.uint8, device=dev) if escape_counts else None
+        rows = torch.empty(self.M, dtype=torch.int32, device=dev)
+        count = torch.zeros(1, dtype=torch.int32, device=dev)
+        check(lib.s12_build_escape_table_async(
+            self.row_offsets.data_ptr(), self.patch_cols.data_ptr(), self.patch_correct.data_ptr(), self.M,
+            self.escape_row_base.data_ptr(), _ptr(self.escape_counts), self.escape_vals.data_ptr(),
+            rows.data_ptr(), count.data_ptr(), _stream(stream)), "s12_build_escape_table_async")
+        self.num_nonempty_rows = int(count.item())
+        self.patch_nonempty_rows = rows[: self.num_nonempty_rows] if self.num_nonempty_rows else None
+
+    @classmethod
+    def load(cls, directory: str, prefix: str, device="cuda", escape_table: bool = True, escape_counts: bool = False,
+             stream=None) -> "CompressedWeight":
+        """Loads ``<prefix>.*`` of a converted model directory with the library's native loader
+        (``s12_load_tensor``: pinned double-buffered uploads, escape table and row list built on the device).
+        Same file family and error behaviour as ``load_compressed`` of engine/model.cpp:32-163."""
+        lib = capi.load()
+        M, K, be, npat = C.c_int(), C.c_int(), C.c_int(), C.c_int64()
+        d, pfx = os.fsencode(directory), prefix.encode()
+        check(lib.s12_tensor_dims(d, pfx, C.byref(M), C.byref(K), C.byref(npat), C.byref(be)), "s12_tensor_dims")
+        M, K, be, npat = M.value, K.value, be.value, npat.value
+        dev = torch.device(device)
+        e = lambda n, dt: torch.empty(n, dtype=dt, device=dev)  # noqa: E731
+        w = cls(M=M, K=K, base_exp=be, split_sm=e(M * K, torch.uint8), split_gr=e((M * K + 1) // 2, torch.uint8))
+        ro = co = cv = wv = rb = ec = ev = ne = None
+        if npat > 0:
+            ro, co, cv, wv = e(M + 1, torch.int32), e(npat, torch.int32), e(npat, torch.int16), e(npat, torch.int16)
+            if escape_table:
+                rb, ev, ne = e(M, torch.int32), e(npat, torch.int16), e(M, torch.int32)
+                ec = e(M * 256, torch.uint8) if escape_counts else None
+        nne = C.c_int(0)
+        with torch.cuda.device(dev):
+            got = lib.s12_load_tensor(d, pfx, w.split_sm.data_ptr(), w.split_gr.data_ptr(), _ptr(ro), _ptr(co), _ptr(cv),
+                                      _ptr(wv), _ptr(rb), _ptr(ec), _ptr(ev), _ptr(ne), C.byref(nne), _stream(stream))
+        if got < 0:
+            check(int(got), "s12_load_tensor")
+        if got > 0:
+            w.num_patches = int(got)
+            w.row_offsets, w.patch_cols, w.patch_correct, w.patch_wrong = ro, co, cv, wv
+            if escape_table:
+                w.escape_row_base, w.escape_counts, w.escape_vals = rb, ec, ev
+                w.num_nonempty_rows = nne.value
+                w.patch_nonempty_rows = ne[: nne.value] if nne.value else None
+        return w
 
     # -- views -----------------------------------------------------------------
     def tensor(self, with_csr: bool = True) -> S12Tensor:
