@@ -277,6 +277,28 @@ int64_t s12_load_tensor(const char* dir, const char* prefix, void* sm, void* gr,
                           void* correct, void* wrong, void* esc_row_base, void* esc_counts, void* esc_vals,
                           void* nonempty_rows, int* num_nonempty, void* stream);
 
+/* =========================================================================
+ * 3c. Mixture of experts (top-2 routing; new: the reference has no MoE path)
+ * ========================================================================= */
+
+/* Routing of T tokens over E <= 32 experts from fp32 router logits [T][E]:
+ * sel[T][2] the two largest logits' experts (ties: lower index), weight[T][2]
+ * the softmax over those two, lists[E][T] every expert's tokens in ascending
+ * order with counts[E], slot[T][2] each choice's position in its list.  All
+ * device int32 / fp32 buffers of the caller.  One launch. */
+int s12_moe_route_async(const void* router_logits, int T, int E, void* sel, void* weight, void* slot, void* lists,
+                        void* counts, void* stream);
+/* xe[E][capacity][K] bf16: row i of expert e = activation row lists[e][i] of
+ * x_bf16 [T][K] for i < counts[e], zero above (choices beyond the capacity are
+ * dropped).  Each expert's block then feeds s12_gemm_async / s12_gemm_multi_async
+ * with B = capacity. */
+int s12_moe_gather_async(const void* x_bf16, int K, int T, int E, int capacity, const void* lists, const void* counts,
+                         void* xe, void* stream);
+/* out[T][H] (+= when accumulate != 0) = sum over a token's two choices of
+ * weight * ye[expert][slot][:], ye fp32 [E][capacity][H]; first choice first. */
+int s12_moe_combine_async(const void* ye, int H, int T, int capacity, const void* sel, const void* weight, const void* slot,
+                          void* out, int accumulate, void* stream);
+
 /* Tensor-parallel shards of a packed tensor (new: the reference is single
  * GPU).  Outputs are caller-allocated for the worst case (all escapes of the
  * source).  Return the shard's escape count, or a negative S12_ERR_*.

@@ -116,3 +116,45 @@ def argmax_engine(logits: np.ndarray) -> int:
                 best_v[tid], best_i[tid] = best_v[tid + s], best_i[tid + s]
         s //= 2
     return int(best_i[0])
+
+
+def moe_route(logits: np.ndarray):
+    """Top-2 routing as published for Mixtral-8x7B (the reference engine has no MoE path; parity unpinned):
+    per token the two largest router logits, ties to the lower expert; weights = softmax over those two.
+    Returns (sel [T,2] int32, weight [T,2] float64).  With a single expert the second choice repeats the
+    first with weight 0."""
+    T, E = logits.shape
+    sel = np.zeros((T, 2), np.int32)
+    wt = np.zeros((T, 2), np.float64)
+    for t in range(T):
+        row = logits[t].astype(np.float64)
+        i1 = int(np.argmax(row))                       # first of the maxima
+        if E == 1:
+            sel[t], wt[t] = (i1, i1), (1.0, 0.0)
+            continue
+        rest = row.copy(); rest[i1] = -np.inf
+        i2 = int(np.argmax(rest))
+        w2 = 1.0 / (1.0 + np.exp(row[i1] - row[i2]))
+        sel[t], wt[t] = (i1, i2), (1.0 - w2, w2)
+    return sel, wt
+
+
+def moe_ffn(x_bf16: np.ndarray, logits: np.ndarray, experts, matmul) -> np.ndarray:
+    """out[t] = sum over the token's two experts of weight * down_e(bf16(silu(gate_e x) * up_e x)), fp32.
+    ``experts[e]`` = (gate, up, down) in whatever form ``matmul(W, x_bf16_rows)`` takes; it returns [rows][M]."""
+    sel, wt = moe_route(logits)
+    T = x_bf16.shape[0]
+    out = None
+    for t in range(T):
+        acc = 0.0
+        for k in range(2):
+            if wt[t, k] == 0.0:
+                continue
+            g, u, d = experts[sel[t, k]]
+            xr = x_bf16[t:t + 1]
+            h = silu_mul_bf16(np.asarray(matmul(g, xr), np.float32), np.asarray(matmul(u, xr), np.float32)).reshape(1, -1)
+            acc = acc + wt[t, k] * np.asarray(matmul(d, h), np.float64)[0]
+        if out is None:
+            out = np.zeros((T, len(acc)), np.float32)
+        out[t] = acc
+    return out

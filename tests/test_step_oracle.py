@@ -57,3 +57,28 @@ def test_rms_norm_and_attention_small():
     out = S.bf16_to_f32(S.attention(q, kc, vc, sk, sv, 1, 4, 2, 8, 8 ** -0.5)).reshape(4, 8)
     for h in range(4):
         np.testing.assert_allclose(out[h], vc[0, h // 2].astype(np.float32) * 0.02, rtol=2 ** -8)
+
+
+def test_moe_route_and_block_statement():
+    """Top-2 routing: ties go to the lower expert, the two weights are the softmax over the two logits; the block
+    is the weighted sum of the chosen experts' SwiGLU outputs."""
+    from oracle import step_oracle as S
+    logits = np.array([[0.0, 2.0, 2.0, -1.0], [1.0, 0.0, 0.0, 0.0], [0.5, 0.5, 0.5, 0.5]], np.float32)
+    sel, wt = S.moe_route(logits)
+    assert sel.tolist() == [[1, 2], [0, 1], [0, 1]]
+    assert np.allclose(wt[0], [0.5, 0.5]) and np.allclose(wt[1], [np.e / (1 + np.e), 1 / (1 + np.e)])
+    sel1, wt1 = S.moe_route(np.zeros((2, 1), np.float32))
+    assert sel1.tolist() == [[0, 0], [0, 0]] and wt1.tolist() == [[1.0, 0.0], [1.0, 0.0]]
+    rng = np.random.default_rng(0)
+    H, F, E = 8, 16, 4
+    experts = [tuple(rng.standard_normal(s) for s in ((F, H), (F, H), (H, F))) for _ in range(E)]
+    x = S.f32_to_bf16(rng.standard_normal((3, H)).astype(np.float32)).reshape(3, H)
+    mm = lambda W, xr: S.bf16_to_f32(xr).astype(np.float64) @ W.T  # noqa: E731
+    out = S.moe_ffn(x, logits, experts, mm)
+    t = 1
+    want = np.zeros(H)
+    for k in range(2):
+        g, u, d = experts[sel[t, k]]
+        h = S.silu_mul_bf16((mm(g, x[t:t + 1])).astype(np.float32), (mm(u, x[t:t + 1])).astype(np.float32)).reshape(1, -1)
+        want += wt[t, k] * mm(d, h)[0]
+    assert np.allclose(out[t], want, rtol=1e-6)

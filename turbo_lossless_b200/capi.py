@@ -52,6 +52,9 @@ SIGNATURES = {
     "s12_version": (_i, []),
     "s12_device_status": (_i, []),
     "s12_host_build_escape_table": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
+    "s12_moe_route_async": (_i, [_vp, _i, _i] + [_vp] * 6),
+    "s12_moe_gather_async": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "s12_moe_combine_async": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),
     "s12_build_escape_table_async": (_i, [_vp] * 3 + [_i] + [_vp] * 6),
     "s12_tensor_dims": (_i, [C.c_char_p, C.c_char_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(C.c_int64), C.POINTER(_i)]),
     "s12_load_tensor": (C.c_int64, [C.c_char_p, C.c_char_p] + [_vp] * 10 + [C.POINTER(_i), _vp]),
