@@ -49,6 +49,10 @@ WORKLOADS = {
                               heads=32, kv_heads=8, position=191, max_seq=256,
                               desc="Llama-3.1-8B-shaped greedy decode step at B=256, every kernel of the step, at position "
                                    "191 (128-token prompts + 128 generated, BASELINE configs[2])"),
+    "mixtral_b64": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=32000, batch=64, experts=8,
+                        desc="Mixtral-8x7B-shaped decode step at B=64 (BASELINE configs[4]): attention projections, top-2 "
+                             "routing over 8 packed SwiGLU experts (0.25% x100 outliers in the expert weights, uniform-random "
+                             "router logits), lm_head; single GPU"),
     "config1": dict(layers=32, hidden=4096, q=4096, kv=0, ffn=0, vocab=0, batch=1,
                     desc="32 distinct 4096x4096 tensors with 0.05% x100 outliers (BASELINE configs[0] shape), one GEMV each"),
 }
@@ -139,11 +143,11 @@ def build_model(cfg, rank, world, layers, torch, CompressedWeight):
     H, Q, KV, F, V = cfg["hidden"], cfg["q"], cfg["kv"], cfg["ffn"], cfg["vocab"]
     outlier = cfg is WORKLOADS["config1"]
 
-    def make(M, K, seed, split):
+    def make(M, K, seed, split, outlier_frac=5e-4 if outlier else 0.0):
         g = torch.Generator(device=dev).manual_seed(seed)
         w = torch.randn(M, K, generator=g, device=dev) * 0.02
-        if outlier:
-            w = torch.where(torch.rand(M, K, generator=g, device=dev) < 5e-4, w * 100.0, w)
+        if outlier_frac:
+            w = torch.where(torch.rand(M, K, generator=g, device=dev) < outlier_frac, w * 100.0, w)
         w = w.to(torch.bfloat16)
         if world > 1 and split == "rows":
             lo, hi = shard(M, rank, world, 16)
@@ -160,7 +164,10 @@ def build_model(cfg, rank, world, layers, torch, CompressedWeight):
         if KV:
             L["wk"], L["wv"] = make(KV, H, s + 2, "rows"), make(KV, H, s + 3, "rows")
             L["wo"] = make(H, Q, s + 4, "cols")
-        if F:
+        if F and cfg.get("experts"):
+            L["experts"] = [{"w_gate": make(F, H, s + 10 * e + 15, None, 2.5e-3), "w_up": make(F, H, s + 10 * e + 16, None, 2.5e-3),
+                             "w_down": make(H, F, s + 10 * e + 17, None, 2.5e-3)} for e in range(cfg["experts"])]
+        elif F:
             L["w_gate"], L["w_up"] = make(F, H, s + 5, "rows"), make(F, H, s + 6, "rows")
             L["w_down"] = make(H, F, s + 7, "cols")
         model["layers"].append(L)
@@ -172,7 +179,12 @@ def build_model(cfg, rank, world, layers, torch, CompressedWeight):
 def model_tensors(model):
     out = []
     for L in model["layers"]:
-        out.extend(L.values())
+        for v in L.values():
+            if isinstance(v, list):                    # experts
+                for ex in v:
+                    out.extend(ex.values())
+            else:
+                out.append(v)
     if model["lm_head"] is not None:
         out.append(model["lm_head"])
     return out
@@ -231,6 +243,14 @@ def run_ours(args):
     x_host = torch.empty(B, H, dtype=torch.int16).pin_memory()
     x_host.copy_(x_hidden.cpu())
     logits_host = torch.empty(logits.shape, dtype=torch.float32).pin_memory()
+
+    moe_blocks, router_logits = [], None
+    if cfg.get("experts"):
+        if world > 1:
+            raise SystemExit("mixtral_b64 runs on one GPU (expert weights are not sharded)")
+        from turbo_lossless_b200.moe import MoEFeedForward
+        router_logits = torch.rand(B, cfg["experts"], generator=gen, device=dev)
+        moe_blocks = [MoEFeedForward(L["experts"], B, eng=eng) for L in model["layers"]]
 
     launches = [0]
 
@@ -291,6 +311,17 @@ def run_ours(args):
                 if world > 1:
                     all_reduce(o_d)
     if model["lm_head"] is not None:
+        add_k(lambda: proj([model["lm_head"]], x_hidden, [logits]))
+    if moe_blocks:
+        # rebuild the layer order with the expert block after each layer's attention projections
+        segments.clear()
+        def moe_layer(L, blk):
+            proj([L["wq"], L["wk"], L["wv"]], x_hidden, [o_q, o_k, o_v])
+            proj([L["wo"]], x_attn, [o_o])
+            blk.forward(x_hidden, router_logits, o_d)
+            launches[0] += blk.launches
+        for L, blk in zip(model["layers"], moe_blocks):
+            add_k(lambda L=L, blk=blk: moe_layer(L, blk))
         add_k(lambda: proj([model["lm_head"]], x_hidden, [logits]))
 
     def step():
