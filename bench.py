@@ -39,6 +39,8 @@ WORKLOADS = {
                          desc="Llama-3.1-8B-shaped decode step at B=256 (BASELINE configs[2]): all split12 projections"),
     "llama70b_b1": dict(layers=80, hidden=8192, q=8192, kv=1024, ffn=28672, vocab=128256, batch=1,
                         desc="Llama-3-70B-shaped decode step at B=1 (BASELINE configs[3]): all split12 projections"),
+    "llama70b_b64": dict(layers=80, hidden=8192, q=8192, kv=1024, ffn=28672, vocab=128256, batch=64,
+                         desc="Llama-3-70B-shaped decode step at B=64 (BASELINE configs[3]): all split12 projections"),
     # the whole decode step (engine/inference.cpp forward loop): the projections plus embed, norms, RoPE + INT8
     # KV store, attention at a mid-generation position, SiLU*up, argmax -- what the reference's tok/s measures
     "mistral7b_b1_full": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=32000, batch=1, full=True,
@@ -291,7 +293,16 @@ def run_ours(args):
         else:
             segments.append(("k", fn))
 
-    for L in model["layers"]:
+    def moe_layer(L, blk):
+        """Attention projections, then the top-2 expert block in place of the dense feed-forward."""
+        proj([L["wq"], L["wk"], L["wv"]], x_hidden, [o_q, o_k, o_v])
+        proj([L["wo"]], x_attn, [o_o])
+        blk.forward(x_hidden, router_logits, o_d)
+        launches[0] += blk.launches
+
+    for L, blk in zip(model["layers"], moe_blocks):
+        add_k(lambda L=L, blk=blk: moe_layer(L, blk))
+    for L in ([] if moe_blocks else model["layers"]):
         if "wk" in L:
             add_k(lambda L=L: proj([L["wq"], L["wk"], L["wv"]], x_hidden, [o_q, o_k, o_v]))
             if use_fused:
@@ -311,17 +322,6 @@ def run_ours(args):
                 if world > 1:
                     all_reduce(o_d)
     if model["lm_head"] is not None:
-        add_k(lambda: proj([model["lm_head"]], x_hidden, [logits]))
-    if moe_blocks:
-        # rebuild the layer order with the expert block after each layer's attention projections
-        segments.clear()
-        def moe_layer(L, blk):
-            proj([L["wq"], L["wk"], L["wv"]], x_hidden, [o_q, o_k, o_v])
-            proj([L["wo"]], x_attn, [o_o])
-            blk.forward(x_hidden, router_logits, o_d)
-            launches[0] += blk.launches
-        for L, blk in zip(model["layers"], moe_blocks):
-            add_k(lambda L=L, blk=blk: moe_layer(L, blk))
         add_k(lambda: proj([model["lm_head"]], x_hidden, [logits]))
 
     def step():

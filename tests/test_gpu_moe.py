@@ -88,3 +88,25 @@ def test_bad_arguments_are_refused():
     assert lib.s12_moe_route_async(None, 4, 8, p, p, p, p, p, None) < 0
     assert lib.s12_moe_gather_async(p, 0, 4, 8, 4, p, p, p, None) < 0
     assert lib.s12_moe_combine_async(p, 8, 4, 0, p, p, p, p, 0, None) < 0
+
+
+@pytest.mark.parametrize("B", [17, 64, 8])
+def test_grouped_gemm_reads_each_tensors_own_rows(O, B):
+    """s12_gemm_grouped_async: six tensors of different heights, each with its own block of B activation rows."""
+    import torch
+    from oracle import step_oracle as S
+    from turbo_lossless_b200 import CompressedWeight, Split12Engine
+    K, Ms = 512, [128, 300, 64, 256, 130, 512]
+    rng = np.random.default_rng(B)
+    raw = [O.synth_weights(M, K, 40 + i, std=0.06, outlier_frac=2e-3) for i, M in enumerate(Ms)]
+    ws = [CompressedWeight.from_packed(O.pack(w)) for w in raw]
+    row0 = [0, B, 2 * B, 2 * B, 5 * B, 3 * B]                        # two tensors share a block, one block is unused
+    x = S.f32_to_bf16(rng.standard_normal((6 * B, K)).astype(np.float32)).reshape(6 * B, K)
+    outs = [torch.full((B, M), np.nan, device="cuda") for M in Ms]
+    eng = Split12Engine()
+    eng.gemm_grouped(ws, torch.from_numpy(x).cuda(), row0, outs, K, B)
+    torch.cuda.synchronize()
+    assert eng.device_status() == 0
+    for w, r, o in zip(raw, row0, outs):
+        want = O.gemm_exact(w, x[r:r + B].view(np.uint16))
+        assert np.abs(o.cpu().numpy() - want).max() <= 1e-3 * np.abs(want).max()

@@ -52,6 +52,7 @@ SIGNATURES = {
     "s12_version": (_i, []),
     "s12_device_status": (_i, []),
     "s12_host_build_escape_table": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
+    "s12_gemm_grouped_async": (_i, [C.POINTER(S12Tensor), _i, _vp, _i, C.POINTER(_i), C.POINTER(_vp), C.POINTER(_i), _i, _vp]),
     "s12_moe_route_async": (_i, [_vp, _i, _i] + [_vp] * 6),
     "s12_moe_gather_async": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "s12_moe_combine_async": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),

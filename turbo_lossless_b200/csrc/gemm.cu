@@ -13,7 +13,7 @@ int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* ou
                    int B, void* stream, const char* who);
 
 int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_stride, void* const* outs,
-                         const int* out_strides, int B, void* stream, const char* who);
+                         const int* out_strides, int B, void* stream, const char* who, const int* act_row0);
 
 int gemm_dispatch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
                   int B, void* stream, const char* who)
@@ -76,10 +76,42 @@ int s12_gemm_multi_async(const S12Tensor* w, int num_tensors, const void* act, i
     }
     if (B == 0) return S12_OK;
     if (B < 0 || !act || act_stride < w[0].K) return fail(S12_ERR_BAD_ARG, "%s: B, act or act_stride", who);
-    if (tc) return gemm_tc_launch_multi(w, num_tensors, act, act_stride, outs, out_strides, B, stream, who);
+    if (tc) return gemm_tc_launch_multi(w, num_tensors, act, act_stride, outs, out_strides, B, stream, who, nullptr);
     for (int i = 0; i < num_tensors; i++) {
         int rc = gemm_dispatch(&w[i], act, act_stride, outs[i], out_strides[i], B, stream, who);
         if (rc) return rc;
+    }
+    return S12_OK;
+}
+
+int s12_gemm_grouped_async(const S12Tensor* w, int num_tensors, const void* act, int act_stride, const int* act_row0,
+                           void* const* outs, const int* out_strides, int B, void* stream)
+{
+    using namespace s12;
+    const char* who = "s12_gemm_grouped_async";
+    if (!w || !outs || !out_strides || !act_row0 || num_tensors < 1) return fail(S12_ERR_BAD_ARG, "%s: bad tensor list", who);
+    if (B == 0) return S12_OK;
+    if (B < 0 || !act || act_stride < w[0].K) return fail(S12_ERR_BAD_ARG, "%s: B, act or act_stride", who);
+    bool tc = B > 16;
+    for (int i = 0; i < num_tensors; i++) {
+        if (w[i].K != w[0].K) return fail(S12_ERR_BAD_ARG, "%s: tensors of one call must share K", who);
+        if (w[i].M < 1 || !outs[i] || out_strides[i] < w[i].M || act_row0[i] < 0)
+            return fail(S12_ERR_BAD_ARG, "%s: tensor %d: M, out, out_stride or act_row0", who, i);
+        tc = tc && gemm_tc_supported(&w[i], act_stride, out_strides[i], B);
+    }
+    // the tensor-core kernel takes four tensors per launch; their row tiles form one schedule
+    for (int i = 0; i < num_tensors; i += 4) {
+        const int n = num_tensors - i < 4 ? num_tensors - i : 4;
+        if (tc) {
+            const int rc = gemm_tc_launch_multi(w + i, n, act, act_stride, outs + i, out_strides + i, B, stream, who, act_row0 + i);
+            if (rc) return rc;
+            continue;
+        }
+        for (int j = i; j < i + n; j++) {
+            const int rc = gemm_dispatch(&w[j], (const uint16_t*)act + (size_t)act_row0[j] * act_stride, act_stride, outs[j],
+                                         out_strides[j], B, stream, who);
+            if (rc) return rc;
+        }
     }
     return S12_OK;
 }

@@ -98,6 +98,7 @@ struct GemmTensor {
     int M, out_stride;
     uint32_t base2;
     int mtile_end;              // exclusive end of this tensor's row tiles in the launch
+    int x_row0;                 // first row of this tensor's sequences in the activation matrix (grouped launches)
 };
 
 struct GemmParams {
@@ -596,15 +597,19 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             grid_dependency_wait();                              // activations come from the predecessor
             int tile = tile0, kb = kb0;
             int mt = tile / P.n_ntiles, nt = tile - mt * P.n_ntiles;
+            int xr0 = P.t[locate_mtile(P, mt).ti].x_row0;        // the tile's tensor may have its own block of sequences
             for (int it = rg.lo; it < rg.hi; it++) {
 #pragma unroll
                 for (int sub = 0; sub < kSub; sub++) {
                     if (it > rg.lo) mbar_wait(b_free + 8 * sub, (uint32_t)(it - rg.lo - 1) & 1, P.status, 0x20u, &s_abort);
                     GT(it - rg.lo, 1 + sub);
                     mbar_arrive_expect_tx(b_full + 8 * sub, xbytes);
-                    tma_load_2d(smem_addr(Xbuf + (size_t)sub * xbytes), &map_x, kb * kBigK + sub * kTK, nt * BN, b_full + 8 * sub);
+                    tma_load_2d(smem_addr(Xbuf + (size_t)sub * xbytes), &map_x, kb * kBigK + sub * kTK, xr0 + nt * BN, b_full + 8 * sub);
                 }
-                if (++kb == KB) { kb = 0; tile++; if (++nt == P.n_ntiles) { nt = 0; mt++; } }
+                if (++kb == KB) {
+                    kb = 0; tile++;
+                    if (++nt == P.n_ntiles) { nt = 0; mt++; xr0 = P.t[locate_mtile(P, mt).ti].x_row0; }
+                }
             }
         }
     } else if (warp == 1) {
@@ -840,7 +845,8 @@ int gemm_tc_supported(const S12Tensor* w, int act_stride, int out_stride, int B)
 // Fills the per-tensor part of the parameters and the tensor maps of up to four
 // tensors that share K and the activations.  Shared by every launch path.
 static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Tensor* w, int nt, const void* act,
-                     int act_stride, void* const* outs, const int* out_strides, int B, const char* who)
+                     int act_stride, void* const* outs, const int* out_strides, int B, const char* who,
+                     const int* act_row0 = nullptr)
 {
     P.nt = nt; P.K = w[0].K; P.B = B;
     P.BN = B >= 256 ? 256 : ((B + 15) / 16) * 16;
@@ -848,7 +854,7 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
     P.n_ntiles = (B + P.BN - 1) / P.BN;
     P.KB = (P.K + kBigK - 1) / kBigK;
     P.neg_base = 0;
-    int mtiles = 0;
+    int mtiles = 0, x_rows = B;
     for (int i = 0; i < nt; i++) {
         const S12Tensor& s = w[i];
         GemmTensor& t = P.t[i];
@@ -856,6 +862,8 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
         t.row_off = csr ? s.row_off : nullptr; t.cols = s.cols; t.correct = s.correct;
         t.out = (float*)outs[i]; t.M = s.M; t.out_stride = out_strides[i];
         t.base2 = make_base2(s.base_exp);
+        t.x_row0 = act_row0 ? act_row0[i] : 0;
+        x_rows = std::max(x_rows, t.x_row0 + B);
         P.neg_base |= s.base_exp < 0;
         mtiles += (s.M + kTileRows - 1) / kTileRows;
         t.mtile_end = mtiles;
@@ -867,7 +875,7 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
     }
     for (int i = nt; i < kMaxGemmTensors; i++) { maps.sm[i] = maps.sm[0]; maps.gr[i] = maps.gr[0]; }
     P.n_mtiles = mtiles;
-    if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)P.K, (uint64_t)B, (uint64_t)act_stride * 2,
+    if (!make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, act, (uint64_t)P.K, (uint64_t)x_rows, (uint64_t)act_stride * 2,
                   kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
     P.tmem_cols = 512u;                  // accumulators below kATmemBase, the A stages above
@@ -974,13 +982,13 @@ static int choose_schedule(GemmParams& P, int max_grid)
 }
 
 int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_stride, void* const* outs,
-                         const int* out_strides, int B, void* stream, const char* who)
+                         const int* out_strides, int B, void* stream, const char* who, const int* act_row0)
 {
     if (reinterpret_cast<uintptr_t>(act) % 16) return fail(S12_ERR_UNSUPPORTED, "%s: activations must be 16-byte aligned", who);
     GemmParams P = {};
     GemmMaps maps;
     CUtensorMap mx;
-    int rc = gemm_fill(P, maps, mx, w, nt, act, act_stride, outs, out_strides, B, who);
+    int rc = gemm_fill(P, maps, mx, w, nt, act, act_stride, outs, out_strides, B, who, act_row0);
     if (rc) return rc;
     P.status = device_status_word();
 
@@ -1004,7 +1012,7 @@ int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* ou
 {
     void* outs[1] = {out};
     int strides[1] = {out_stride};
-    return gemm_tc_launch_multi(w, 1, act, act_stride, outs, strides, B, stream, who);
+    return gemm_tc_launch_multi(w, 1, act, act_stride, outs, strides, B, stream, who, nullptr);
 }
 
 }  // namespace s12

@@ -345,6 +345,18 @@ class Split12Engine:
         check(self.lib.s12_gemm_multi_async(arr, n, _ptr(bf16_in), act_stride, optr, strides, bs, _stream(stream)),
               "s12_gemm_multi_async")
 
+    def gemm_grouped(self, ws: Sequence[CompressedWeight], bf16_in: torch.Tensor, act_row0: Sequence[int],
+                     outs: Sequence[torch.Tensor], act_stride: int, bs: int, stream=None, exact: bool = True) -> None:
+        """Tensors that share K, each reading its own block of ``bs`` rows of ``bf16_in`` starting at
+        ``act_row0[i]`` (the experts of an MoE layer): four tensors per tensor-core launch."""
+        n = len(ws)
+        arr = (S12Tensor * n)(*[w.tensor(with_csr=exact) for w in ws])
+        optr = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+        strides = (C.c_int * n)(*[o.stride(0) for o in outs])
+        rows = (C.c_int * n)(*[int(r) for r in act_row0])
+        check(self.lib.s12_gemm_grouped_async(arr, n, _ptr(bf16_in), act_stride, rows, optr, strides, bs, _stream(stream)),
+              "s12_gemm_grouped_async")
+
     def gemm_noalloc(self, w: CompressedWeight, bf16_in: torch.Tensor, out: torch.Tensor, act_stride: int,
                      out_stride: int, bs: int, stream=None, exact: bool = True) -> None:
         """s12_gemm_async for callers that may not allocate: scratch is a fixed array in the library."""

@@ -2,7 +2,7 @@
 
 The reference engine has no MoE path; this block follows the published Mixtral algorithm (the two largest
 router logits per token, softmax over those two, SwiGLU experts) and runs as launches of the CUDA library
-only: route -> gather by expert -> per expert gate/up (one launch), SiLU*up, down -> combine.  Every expert
+only: route -> gather by expert -> gate/up of all experts (grouped launches), SiLU*up, down (grouped) -> combine.  Every expert
 works on a dense block of ``capacity`` rows (zero rows above its token count), so nothing depends on a
 count read back by the host and the whole block can sit inside a captured CUDA graph.
 """
@@ -43,7 +43,11 @@ class MoEFeedForward:
 
     @property
     def launches(self) -> int:
-        return 3 + 3 * self.E
+        """Kernel launches of one forward call: route, gather, combine, SiLU*up and the projections -- four tensors
+        per launch on the tensor cores (capacity > 16), one per tensor and 16 rows otherwise."""
+        if self.cap > 16:
+            return 4 + (2 * self.E + 3) // 4 + (self.E + 3) // 4
+        return 4 + 3 * self.E * ((self.cap + 15) // 16)
 
     def forward(self, x_bf16: torch.Tensor, router_logits: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
                 stream=None) -> None:
@@ -54,15 +58,15 @@ class MoEFeedForward:
                                       _ptr(self.lists), _ptr(self.counts), st), "s12_moe_route_async")
         check(lib.s12_moe_gather_async(_ptr(x_bf16), self.H, T, E, cap, _ptr(self.lists), _ptr(self.counts), _ptr(self.xe), st),
               "s12_moe_gather_async")
+        # all experts' gate/up as grouped launches (expert i reads rows [i*cap, (i+1)*cap) of xe), one SiLU*up over
+        # all blocks, all experts' down projections as grouped launches
+        ws, rows, outs = [], [], []
         for i, w in enumerate(self.experts):
-            self._proj([w["w_gate"], w["w_up"]], self.xe[i], [self.gate[i], self.up[i]], stream)
-            e.silu_mul_bf16(self.gate[i], self.up[i], self.he[i], self.F, cap, stream=stream)
-            self._proj([w["w_down"]], self.he[i], [self.ye[i]], stream)
+            ws += [w["w_gate"], w["w_up"]]; rows += [i * cap, i * cap]; outs += [self.gate[i], self.up[i]]
+        e.gemm_grouped(ws, self.xe, rows, outs, self.H, cap, stream=stream)
+        e.silu_mul_bf16(self.gate, self.up, self.he, self.F, E * cap, stream=stream)
+        e.gemm_grouped([w["w_down"] for w in self.experts], self.he, [i * cap for i in range(E)],
+                       [self.ye[i] for i in range(E)], self.F, cap, stream=stream)
         check(lib.s12_moe_combine_async(_ptr(self.ye), self.H, T, cap, _ptr(self.sel), _ptr(self.weight), _ptr(self.slot),
                                         _ptr(out), int(accumulate), st), "s12_moe_combine_async")
 
-    def _proj(self, ws, x, outs, stream):
-        if self.cap == 1:
-            self.eng.gemv(ws, x, outs, stream=stream)
-        else:
-            self.eng.gemm_multi(ws, x, outs, x.stride(0), self.cap, stream=stream)
