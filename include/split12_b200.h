@@ -280,7 +280,7 @@ int64_t s12_load_tensor(const char* dir, const char* prefix, void* sm, void* gr,
 /* Grouped form: any number of tensors that share K, each with its OWN block of
  * B activation rows inside one matrix: tensor i reads rows [act_row0[i],
  * act_row0[i] + B) of act (host array of row indices; blocks may coincide, as
- * for an expert's gate and up).  Four tensors per tensor-core launch, their
+ * for an expert's gate and up).  Eight tensors per tensor-core launch, their
  * row tiles in one schedule.  The experts of a mixture-of-experts layer run as
  * a few launches this way instead of one per expert and projection. */
 int s12_gemm_grouped_async(const S12Tensor* w, int num_tensors, const void* act, int act_stride, const int* act_row0,

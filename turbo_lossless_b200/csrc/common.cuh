@@ -13,6 +13,8 @@ namespace s12 {
 int  fail(int code, const char* fmt, ...);          // records the message, returns code
 int  check_cuda(cudaError_t e, const char* what);   // S12_OK or S12_ERR_CUDA
 bool dependent_launch_enabled();
+// tensors that one launch of the tensor-core GEMM takes (their tensor maps travel as kernel parameters)
+constexpr int kMaxGemmTensors = 8;
 int  sm_count();                                    // SMs of the current device (cached)
 unsigned int* device_status_word();                 // per-device status word (device pointer)
 

@@ -99,9 +99,9 @@ int s12_gemm_grouped_async(const S12Tensor* w, int num_tensors, const void* act,
             return fail(S12_ERR_BAD_ARG, "%s: tensor %d: M, out, out_stride or act_row0", who, i);
         tc = tc && gemm_tc_supported(&w[i], act_stride, out_strides[i], B);
     }
-    // the tensor-core kernel takes four tensors per launch; their row tiles form one schedule
-    for (int i = 0; i < num_tensors; i += 4) {
-        const int n = num_tensors - i < 4 ? num_tensors - i : 4;
+    // the tensor-core kernel takes kMaxGemmTensors tensors per launch; their row tiles form one schedule
+    for (int i = 0; i < num_tensors; i += kMaxGemmTensors) {
+        const int n = num_tensors - i < kMaxGemmTensors ? num_tensors - i : kMaxGemmTensors;
         if (tc) {
             const int rc = gemm_tc_launch_multi(w + i, n, act, act_stride, outs + i, out_strides + i, B, stream, who, act_row0 + i);
             if (rc) return rc;

@@ -88,7 +88,6 @@ __device__ __forceinline__ unsigned long long gt_now() { unsigned long long t; a
 #define GP(slot) do { } while (0)
 #endif
 
-constexpr int kMaxGemmTensors = 4;       // tensors sharing K and the activations in one launch (q/k/v, gate/up)
 
 struct GemmTensor {
     const int32_t* row_off;     // null: escapes stay "wrong"
@@ -842,8 +841,8 @@ int gemm_tc_supported(const S12Tensor* w, int act_stride, int out_stride, int B)
     return encode_fn() != nullptr;
 }
 
-// Fills the per-tensor part of the parameters and the tensor maps of up to four
-// tensors that share K and the activations.  Shared by every launch path.
+// Fills the per-tensor part of the parameters and the tensor maps of up to kMaxGemmTensors
+// tensors that share K (and the activations, or one block of activation rows each).  Shared by every launch path.
 static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Tensor* w, int nt, const void* act,
                      int act_stride, void* const* outs, const int* out_strides, int B, const char* who,
                      const int* act_row0 = nullptr)

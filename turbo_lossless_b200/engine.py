@@ -348,7 +348,7 @@ class Split12Engine:
     def gemm_grouped(self, ws: Sequence[CompressedWeight], bf16_in: torch.Tensor, act_row0: Sequence[int],
                      outs: Sequence[torch.Tensor], act_stride: int, bs: int, stream=None, exact: bool = True) -> None:
         """Tensors that share K, each reading its own block of ``bs`` rows of ``bf16_in`` starting at
-        ``act_row0[i]`` (the experts of an MoE layer): four tensors per tensor-core launch."""
+        ``act_row0[i]`` (the experts of an MoE layer): eight tensors per tensor-core launch."""
         n = len(ws)
         arr = (S12Tensor * n)(*[w.tensor(with_csr=exact) for w in ws])
         optr = (C.c_void_p * n)(*[o.data_ptr() for o in outs])

@@ -43,10 +43,10 @@ class MoEFeedForward:
 
     @property
     def launches(self) -> int:
-        """Kernel launches of one forward call: route, gather, combine, SiLU*up and the projections -- four tensors
+        """Kernel launches of one forward call: route, gather, combine, SiLU*up and the projections -- eight tensors
         per launch on the tensor cores (capacity > 16), one per tensor and 16 rows otherwise."""
         if self.cap > 16:
-            return 4 + (2 * self.E + 3) // 4 + (self.E + 3) // 4
+            return 4 + (2 * self.E + 7) // 8 + (self.E + 7) // 8
         return 4 + 3 * self.E * ((self.cap + 15) // 16)
 
     def forward(self, x_bf16: torch.Tensor, router_logits: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
