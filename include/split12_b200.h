@@ -183,8 +183,14 @@ int s12_gemv_async(const S12Tensor* w, int num_tensors, const void* act,
 int s12_gemv_batched_async(const S12Tensor* w, const void* act, int act_stride,
                            void* out, int out_stride, int B, void* stream);
 
-/* Batched decode + GEMM on the tensor cores, any B >= 1 (dispatches to the
- * GEMV family for small B).  Exact escapes when w carries its CSR list. */
+/* Batched decode + GEMM, any B >= 1 (dispatches by B: the GEMV family for
+ * B <= 16, the streaming kernel for 16 < B <= 128, the tensor cores above).
+ * Exact escapes when w carries its CSR list.
+ * All s12_gemm_* / nv_launch_split12_*gemm* calls of one device share one
+ * partial-tile workspace (allocated by s12_init or by the first such call):
+ * launches that may overlap on the GPU (different streams without an event
+ * between them) would mix their partial tiles and must be serialised by the
+ * caller.  The engine issues them from one stream. */
 int s12_gemm_async(const S12Tensor* w, const void* act, int act_stride,
                    void* out, int out_stride, int B, void* stream);
 
@@ -213,7 +219,10 @@ int s12_gemm_multi_async(const S12Tensor* w, int num_tensors, const void* act, i
  * on it and must be serialised by the caller.  Nothing in the 8 MiB array
  * needs to start at zero (every partial is written before it is read in the
  * same call); the hand-over counters of the partials sit in a second, 1 KB
- * static array that starts at zero and is left at zero by every call. */
+ * static array that starts at zero and is left at zero by every call.  A
+ * bounded wait that gives up inside such a call is reported by
+ * s12_device_status() like any other (the call keeps its own status word in
+ * the library image; s12_device_status reads and clears both). */
 int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int act_stride,
                            void* out, int out_stride, int B, void* stream);
 
@@ -223,12 +232,21 @@ int s12_gemm_noalloc_async(const S12Tensor* w, const void* act, int act_stride,
  * for the predecessor's results.  Off by default.  Returns the old setting. */
 int s12_set_dependent_launch(int enable);
 
+/* Optional per-device set-up, with the device current: allocates the status
+ * word and the GEMM's partial-tile workspace (148 x 128 KB) and sets the
+ * kernels' attributes, so that no later call allocates or synchronises.
+ * Without it the first call that needs them does the same work (cudaMalloc,
+ * which synchronises the device).  Call it before any stream capture. */
+int s12_init(void);
+
 /* Text of the last error on this thread ("" if none). */
 const char* s12_last_error(void);
 /* Library version: major*10000 + minor*100 + patch. */
 int s12_version(void);
 /* Reads and clears the device-side status word of the current device
- * (0 = ok; non-zero = a bounded wait expired; bits name the site).
+ * (0 = ok; non-zero = a bounded wait expired; bits name the site), including
+ * the word of s12_gemm_noalloc_async.  When it was non-zero the GEMM's
+ * hand-over counters are zeroed again, so later launches start clean.
  * Synchronises the device. */
 int s12_device_status(void);
 
@@ -361,9 +379,11 @@ int s12_pack_fill_async(const void* bf16, int M, int K, int base_exp, const void
  *   launch_silu_mul_bf16_batch, launch_add_batch       :463-493
  *   launch_attention_all_heads, ..._batch              :589, :695
  *   launch_rope_batch, launch_store_kv_batch           :848, :860
- * Not provided: launch_flash_attention[_batch] (:1107, :1120; the engine takes
- * that route only from position 1024 on; launch_attention_all_heads here has
- * no such length limit below ~50k positions). */
+ *   launch_flash_attention, ..._batch                  :1107, :1120
+ * The engine takes the flash names from position 1024 on; here they forward to
+ * the same kernels as launch_attention_all_heads[_batch], which cut long
+ * contexts into up to 8 slices (about 60k positions at 4 query heads per kv
+ * head; beyond that S12_ERR_TOO_LARGE). */
 int launch_embed_lookup(const int16_t* embd_table, const int* token_ids, float* output, int n_embd,
                         int batch_size, int n_vocab, void* stream);
 int launch_argmax(const float* logits, int* result, int n, void* stream);
@@ -391,6 +411,14 @@ int launch_attention_all_heads_batch(const float* q, const int8_t* kv_k, const i
                                      const float* kv_scale_k, const float* kv_scale_v, int16_t* output,
                                      const int* positions, int n_head, int n_head_kv, int head_dim,
                                      int max_seq, float scale, int batch_size, int kv_stride, void* stream);
+int launch_flash_attention(const float* q, const int8_t* k_cache, const int8_t* v_cache,
+                           const float* kv_scale_k, const float* kv_scale_v, int16_t* output,
+                           int n_head, int n_head_kv, int head_dim, int seq_len, int max_seq,
+                           float scale, void* stream);
+int launch_flash_attention_batch(const float* q, const int8_t* kv_k, const int8_t* kv_v,
+                                 const float* kv_scale_k, const float* kv_scale_v, int16_t* output,
+                                 const int* positions, int n_head, int n_head_kv, int head_dim,
+                                 int max_seq, float scale, int batch_size, int kv_stride, void* stream);
 /* launch_store_kv_batch with a cache per sequence: sequence s writes at
  * kv_k + s * kv_stride (int8 elements; scales at s * kv_stride / head_dim), the
  * layout launch_attention_all_heads_batch reads.  The engine's own batched
@@ -439,6 +467,15 @@ int s12_allreduce_f32_async(S12Comm* comm, const void* in, void* out, int n, voi
  * multiple of 4, <= max_floats.  Falls back to s12_gemv_async followed by
  * s12_allreduce_f32_async when the streaming kernel does not take the shape. */
 int s12_gemv_allreduce_async(S12Comm* comm, const S12Tensor* w, const void* act, void* out, void* stream);
+/* How long a kernel of this communicator waits for a peer before it gives up
+ * (default 2000 ms).  Returns the old limit in ms.  A call that gave up sets
+ * bit 0x8000 of the status word, stores sums that lack the missing ranks and
+ * leaves the communicator's call counters out of step with the peers'. */
+int s12_comm_set_wait_limit_ms(S12Comm* comm, int ms);
+/* After a call that gave up: zeroes this rank's receive areas and call counter
+ * (synchronises the device).  Every rank calls it, with a host-side barrier
+ * before and after, then the communicator is usable again. */
+int s12_comm_reset(S12Comm* comm);
 int s12_comm_destroy(S12Comm* comm);
 /* Test support for a single GPU: `world` communicators created in one process
  * on one device are wired to each other, and one cooperative launch runs all

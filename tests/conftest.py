@@ -4,6 +4,10 @@ import sys
 import numpy as np
 import pytest
 
+# The library honours its S12_* tuning knobs only when this is set before its first launch; the tests use the
+# knobs to force every kernel variant and schedule.
+os.environ.setdefault("S12_TUNE", "1")
+
 ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

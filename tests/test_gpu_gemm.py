@@ -126,3 +126,102 @@ def test_every_schedule_gives_the_oracle_result(eng, O, monkeypatch, knobs, M, K
     ref = O.gemm_exact(w, x)
     assert np.abs(outs[0] - ref).max() <= REL_TOL * np.abs(ref).max()
     np.testing.assert_array_equal(outs[0], outs[1])
+
+
+def _tiled(O, p, tiles):
+    """`tiles` copies of a packed slab stacked into one tall tensor (CSR offsets shifted per copy)."""
+    ro = np.concatenate([[0]] + [p.row_off[1:].astype(np.int64) + t * p.num_patches for t in range(tiles)])
+    return O.Packed(p.M * tiles, p.K, p.base_exp, np.tile(p.sm, tiles), np.tile(p.gr, tiles), ro.astype(np.int32),
+                    np.tile(p.cols, tiles), np.tile(p.correct, tiles), np.tile(p.wrong, tiles))
+
+
+@pytest.mark.parametrize("rows,tiles,K,B", [(4096, 1, 14336, 256),      # down projection: 56 raw stages per tile
+                                            (4008, 32, 4096, 256),      # lm_head 128256 x 4096: 1002 tiles, many per CTA
+                                            (4096, 1, 4096, 128),
+                                            (1024, 1, 8192, 64),        # 70B k/v projection
+                                            (512, 1, 28672, 64)])       # 70B down projection (K = 28672)
+def test_benchmark_shapes(eng, O, rows, tiles, K, B):
+    """The largest launches of the B=256 and 70B benchmarks.  The oracle packs one slab of `rows` rows; the
+    device tensor is `tiles` copies of it, so every copy's output block must equal the slab's oracle result."""
+    w = O.synth_weights(rows, K, rows + K + B, outlier_frac=5e-4)
+    p = O.pack(w)
+    x = O.synth_acts(B, K, 21)
+    big = _tiled(O, p, tiles) if tiles > 1 else p
+    M = rows * tiles
+    out = torch.full((B, M), float("nan"), device="cuda")
+    eng.gemm(_cw(big, escape_table=False), dev(x), out, K, M, B)
+    assert eng.device_status() == 0
+    ref = O.gemm_exact(w, x)
+    got = out.cpu().numpy()
+    for t in range(tiles):
+        assert_close(got[:, t * rows:(t + 1) * rows], ref, what=f"copy {t}")
+
+
+def _tiny_exponent_weights(M, K, seed, escapes):
+    """bf16 patterns whose exponent fields lie in 1..14 (plus exact zeros), so that the packer's window starts at
+    exponent 0 and base_exp is -1; `escapes` adds a few values above the window."""
+    rng = np.random.default_rng(seed)
+    w = ((rng.integers(0, 2, (M, K)) << 15) | (rng.integers(1, 15, (M, K)) << 7) | rng.integers(0, 128, (M, K))).astype(np.uint16)
+    w[rng.random((M, K)) < 0.02] = 0
+    if escapes:
+        mask = rng.random((M, K)) < 2e-3
+        w[mask] = ((rng.integers(15, 19, (M, K)) << 7) | rng.integers(0, 128, (M, K))).astype(np.uint16)[mask]
+    return w
+
+
+@pytest.mark.parametrize("B", [24, 256])
+@pytest.mark.parametrize("escapes", [False, True])
+def test_window_starting_at_exponent_zero(eng, O, B, escapes):
+    """base_exp = -1 (split12_pack.c:29-35) through the batched kernels: exact with the CSR list; without it
+    escapes keep the reference's bits (exponent field 0xFF: infinities and NaNs in their rows)."""
+    M, K = 300, 512
+    w = _tiny_exponent_weights(M, K, 5 + B, escapes)
+    p = O.pack(w)
+    assert p.base_exp == -1 and (p.num_patches > 0) == escapes
+    x = (O.synth_acts(B, K, 4) + np.uint16(100 << 7)).astype(np.uint16)      # activations * 2^100: products are normal fp32
+    xd = dev(x)
+    out = torch.full((B, M), float("nan"), device="cuda")
+    eng.gemm(_cw(p), xd, out, K, M, B)
+    assert_close(out, O.gemm_exact(w, x), what="with the CSR list")
+    out2 = torch.full((B, M), float("nan"), device="cuda")
+    eng.gemm_only(_cw(p), xd, out2, K, M, B)                                  # null patch pointers
+    ref = O.gemm_twopass(p, x, patches=False)
+    got = out2.cpu().numpy()
+    fin = np.isfinite(ref)
+    assert np.array_equal(np.isfinite(got), fin)
+    if escapes:
+        assert not fin.all()
+    scale = np.abs(ref[fin]).max()
+    assert np.abs(got[fin] - ref[fin]).max() <= REL_TOL * scale
+    assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("knobs", [{}, {"S12_GEMM_CLUSTER": "0", "S12_GEMM_SPLIT": "0"}, {"S12_GEMM_CLUSTER": "2"}])
+@pytest.mark.parametrize("B", [257, 300, 512])
+def test_more_than_one_tile_of_sequences(eng, O, monkeypatch, knobs, B):
+    """B > 256: several sequence tiles per row tile (tile -> (row tile, sequence tile) decomposition, drain
+    offsets, stream-K ownership across sequence tiles), on the default, stream-K and cluster schedules."""
+    for k, v in knobs.items():
+        monkeypatch.setenv(k, v)
+    M, K = 700, 1024
+    w, p, x = _case(O, M, K, B, B, frac=2e-3)
+    out = torch.full((B, M + 4), float("nan"), device="cuda")
+    eng.gemm(_cw(p), dev(x), out, K, M + 4, B)
+    assert_close(out[:, :M], O.gemm_exact(w, x), what=f"B={B}")
+    assert torch.isnan(out[:, M:]).all()
+    assert eng.device_status() == 0
+
+
+def test_grouped_launch_with_several_sequence_tiles(eng, O):
+    K, B = 512, 300
+    specs = [(256, 0), (130, 300), (384, 0)]                 # (rows, first activation row)
+    x = O.synth_acts(2 * B, K, 31)
+    ws, cws = [], []
+    for i, (M, _) in enumerate(specs):
+        w = O.synth_weights(M, K, 300 + i, outlier_frac=1e-3)
+        ws.append(w); cws.append(_cw(O.pack(w)))
+    outs = [torch.full((B, M), float("nan"), device="cuda") for M, _ in specs]
+    eng.gemm_grouped(cws, dev(x), [r0 for _, r0 in specs], outs, K, B)
+    for w, (M, r0), o in zip(ws, specs, outs):
+        assert_close(o, O.gemm_exact(w, x[r0:r0 + B]), what=f"M={M} rows from {r0}")
+    assert eng.device_status() == 0

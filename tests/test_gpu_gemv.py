@@ -28,7 +28,10 @@ def _case(O, M, K, seed, frac=5e-4, B=1):
 
 
 SHAPES = [(16, 128), (1, 32), (2, 64), (15, 96), (17, 160), (130, 256), (64, 4096), (33, 14336),
-          (4096, 4096), (1024, 4096), (1000, 1056), (257, 11008), (4099, 4096), (2050, 14336)]
+          (4096, 4096), (1024, 4096), (1000, 1056), (257, 11008), (4099, 4096), (2050, 14336),
+          # Llama-3-70B row lengths: K = 8192 (two CTAs per SM) and K = 28672, whose activation vector leaves
+          # room for one CTA per SM only in the streaming kernel
+          (64, 8192), (1000, 8192), (64, 28672), (1000, 28672)]
 
 
 @pytest.mark.parametrize("M,K", SHAPES)
@@ -48,7 +51,7 @@ def test_legacy_two_pass_b1(eng, O, M, K):
     assert torch.equal(out, out2)
 
 
-@pytest.mark.parametrize("M,K", [(16, 128), (130, 256), (14336, 4096)])
+@pytest.mark.parametrize("M,K", [(16, 128), (130, 256), (14336, 4096), (1000, 8192)])
 def test_legacy_dual(eng, O, M, K):
     wa, pa, x = _case(O, M, K, 31, frac=1e-3)
     wb = O.synth_weights(M, K, 32, std=0.05)

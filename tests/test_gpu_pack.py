@@ -45,3 +45,20 @@ def test_pack_then_decompress_roundtrip_full_size():
     assert 0 < cw.num_patches < 0.001 * w.numel()
     out = Split12Engine().decompress(cw)
     assert torch.equal(out, w.view(torch.int16))
+
+
+def test_pack_under_dependent_launch(O, golden):
+    """The packer's five kernels each consume their predecessor's output; with programmatic dependent launch
+    enabled every one of them waits for it before reading."""
+    from turbo_lossless_b200 import CompressedWeight, Split12Engine
+    eng = Split12Engine()
+    old = eng.set_dependent_launch(True)
+    try:
+        for name in GOLDEN_CASES:
+            w, ref = golden_packed(O, golden, name)
+            _check(CompressedWeight.pack_on_device(dev(w)), ref)
+        w = O.synth_weights(3000, 4096, 3, outlier_frac=1e-2)
+        for _ in range(3):
+            _check(CompressedWeight.pack_on_device(dev(w)), O.pack(w))
+    finally:
+        eng.set_dependent_launch(old)

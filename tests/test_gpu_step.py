@@ -189,3 +189,55 @@ def test_batched_rope_store_attention_per_sequence_caches(eng, S):
         ref = S.attention(q_last[s], ref_k[s], ref_v[s], ref_sk[s], ref_sv[s], int(pos_last[s]) + 1, n_head, n_head_kv, hd, scale)
         want = S.bf16_to_f32(ref).astype(np.float64)
         assert np.abs(got[s] - want).max() <= 2.0 ** -7 * np.abs(want).max()
+
+
+def test_flash_attention_names_forward_to_the_same_kernels(eng, S):
+    """The engine calls launch_flash_attention[_batch] from position 1024 on (engine/inference.cpp:285,432):
+    same arguments, same results as launch_attention_all_heads[_batch], checked against the oracle at 1500
+    positions, and at 9000 positions for 80 (sequence, kv head) pairs with four query heads each: one slice's
+    scores no longer fit a CTA's shared memory, so the positions are cut in two although the GPU is already full."""
+    import torch
+    n_head, n_head_kv, hd, max_seq, seq_len = 32, 8, 128, 2048, 1500
+    rng = np.random.default_rng(77)
+    q = rng.standard_normal(n_head * hd).astype(np.float32)
+    kc = rng.integers(-127, 128, (max_seq, n_head_kv, hd)).astype(np.int8)
+    vc = rng.integers(-127, 128, (max_seq, n_head_kv, hd)).astype(np.int8)
+    sk = (rng.random((max_seq, n_head_kv)) * 0.02 + 0.001).astype(np.float32)
+    sv = (rng.random((max_seq, n_head_kv)) * 0.02 + 0.001).astype(np.float32)
+    scale = float(1.0 / np.sqrt(hd))
+    qd, kd, vd, skd, svd = _cuda(q), _cuda(kc), _cuda(vc), _cuda(sk), _cuda(sv)
+    out = torch.zeros(n_head * hd, dtype=torch.int16, device="cuda")
+    out2 = torch.zeros_like(out)
+    eng.attention_all_heads(qd, kd, vd, skd, svd, out, n_head, n_head_kv, hd, seq_len, max_seq, scale)
+    st = torch.cuda.current_stream().cuda_stream
+    rc = eng.lib.launch_flash_attention(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), skd.data_ptr(), svd.data_ptr(),
+                                        out2.data_ptr(), n_head, n_head_kv, hd, seq_len, max_seq, scale, st)
+    assert rc == 0
+    assert torch.equal(out, out2)
+    want = S.bf16_to_f32(S.attention(q, kc, vc, sk, sv, seq_len, n_head, n_head_kv, hd, scale)).astype(np.float64)
+    got = S.bf16_to_f32(out2.cpu().numpy()).astype(np.float64)
+    assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()
+
+    # batched name, long context, many sequences
+    batch, n_head, n_head_kv, long_seq = 20, 16, 4, 9000
+    kv_stride = long_seq * n_head_kv * hd
+    qb = rng.standard_normal((batch, n_head * hd)).astype(np.float32)
+    kcb = rng.integers(-127, 128, (batch, long_seq, n_head_kv, hd)).astype(np.int8)
+    vcb = rng.integers(-127, 128, (batch, long_seq, n_head_kv, hd)).astype(np.int8)
+    skb = (rng.random((batch, long_seq, n_head_kv)) * 0.02 + 0.001).astype(np.float32)
+    svb = (rng.random((batch, long_seq, n_head_kv)) * 0.02 + 0.001).astype(np.float32)
+    pos = rng.integers(7000, long_seq, batch).astype(np.int32)
+    pos[0] = long_seq - 1
+    outb = torch.zeros((batch, n_head * hd), dtype=torch.int16, device="cuda")
+    rc = eng.lib.launch_flash_attention_batch(_cuda(qb).data_ptr(), _cuda(kcb).data_ptr(), _cuda(vcb).data_ptr(),
+                                              _cuda(skb).data_ptr(), _cuda(svb).data_ptr(), outb.data_ptr(),
+                                              _cuda(pos).data_ptr(), n_head, n_head_kv, hd, long_seq, scale, batch,
+                                              kv_stride, st)
+    assert rc == 0, eng.lib.s12_last_error()
+    torch.cuda.synchronize()
+    for s in (0, 7, batch - 1):
+        want = S.bf16_to_f32(S.attention(qb[s], kcb[s], vcb[s], skb[s], svb[s], int(pos[s]) + 1, n_head, n_head_kv, hd,
+                                         scale)).astype(np.float64)
+        got = S.bf16_to_f32(outb[s].cpu().numpy()).astype(np.float64)
+        assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()
+    assert eng.device_status() == 0

@@ -77,6 +77,71 @@ def test_fused_gemv_allreduce_world_of_one(M, K):
     comm.close()
 
 
+@pytest.mark.parametrize("M,K,offset", [(1000, 1000, 0),      # K not a multiple of 32: the general GEMV path
+                                        (1024, 1024, 4),      # activations 8 bytes off a 16-byte boundary
+                                        (4096, 64, 0)])       # too small for the streaming kernel
+def test_gemv_allreduce_on_shapes_the_streaming_kernel_refuses(M, K, offset):
+    """Every route through s12_gemv_allreduce_async ends in the sum over ranks (here a world of one, where the
+    all-reduce kernel must leave the values as they are and advance the communicator's call counter like the
+    fused path does: the calls alternate between both routes and stay in step)."""
+    import torch
+    from oracle import oracle as O
+    from turbo_lossless_b200 import CompressedWeight, Split12Engine, TPComm
+    eng = Split12Engine()
+    (comm,) = TPComm.local(1, 8192)
+    w = O.synth_weights(M, K, 6, outlier_frac=2e-3)
+    cw = CompressedWeight.from_packed(O.pack(w))
+    big = O.synth_weights(4096, 4096, 7)
+    cbig = CompressedWeight.from_packed(O.pack(big))
+    for call in range(3):
+        x = O.synth_acts(1, K, 50 + call)
+        buf = torch.zeros(K + 8, dtype=torch.int16, device="cuda")
+        buf[offset:offset + K] = torch.from_numpy(x[0].view(np.int16)).cuda()
+        out = torch.full((M,), float("nan"), device="cuda")
+        comm.gemv_all_reduce(cw, buf[offset:offset + K], out)
+        xb = O.synth_acts(1, 4096, 60 + call)
+        outb = torch.full((4096,), float("nan"), device="cuda")
+        comm.gemv_all_reduce(cbig, torch.from_numpy(xb.view(np.int16)).cuda(), outb)   # the fused route in between
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        ref = O.gemm_exact(w, x)[0]
+        np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=0, atol=1e-4 * np.abs(ref).max())
+        refb = O.gemm_exact(big, xb)[0]
+        np.testing.assert_allclose(outb.cpu().numpy(), refb, rtol=0, atol=1e-4 * np.abs(refb).max())
+    comm.close()
+
+
+@pytest.mark.parametrize("n", [4096, 65536])
+def test_wait_for_a_peer_that_never_arrives_runs_out(n):
+    """Rank 0 of a world of two calls the all-reduce alone with a 5 ms limit: the kernel returns, the status word
+    carries 0x8000, and after both ranks reset their communicators a complete call gives the exact sum.
+    (Both forms of the kernel: words with tokens for small vectors, flags for large ones.)"""
+    import torch
+    from turbo_lossless_b200 import TPComm, Split12Engine
+    eng = Split12Engine()
+    comms = TPComm.local(2, 70000)
+    assert comms[0].set_wait_limit_ms(5) == 2000
+    x = torch.ones(n, device="cuda")
+    out = torch.empty(n, device="cuda")
+    comms[0].all_reduce(x, out)                # nobody plays rank 1: nothing ever sets the awaited words
+    torch.cuda.synchronize()
+    assert eng.device_status() & 0x8000
+    assert eng.device_status() == 0            # reading cleared it
+    for c in comms:
+        c.reset()
+    comms[0].set_wait_limit_ms(2000)
+    parts = [np.random.default_rng(r).standard_normal(n).astype(np.float32) for r in range(2)]
+    srcs = [torch.from_numpy(p).cuda() for p in parts]
+    dsts = [torch.full((n,), float("nan"), device="cuda") for _ in range(2)]
+    TPComm.all_reduce_emulated(comms, srcs, dsts)
+    torch.cuda.synchronize()
+    assert eng.device_status() == 0
+    for d in dsts:
+        np.testing.assert_array_equal(d.cpu().numpy(), parts[0] + parts[1])
+    for c in comms:
+        c.close()
+
+
 _WORKER = r"""
 import os, sys
 import numpy as np, torch, torch.distributed as dist
@@ -100,7 +165,7 @@ for call, n in enumerate([4096, 4096, 14336, 1 << 20, 4096]):
 # row-parallel GEMV fused with its all-reduce: each rank holds a column slice of W
 from oracle import oracle as O
 from turbo_lossless_b200 import CompressedWeight
-for call, (M, K) in enumerate([(4096, 4096), (4096, 14336), (1000, 1024)]):
+for call, (M, K) in enumerate([(4096, 4096), (4096, 14336), (1000, 1024), (1000, 2000)]):   # last: K/world % 32 != 0
     w = O.synth_weights(M, K, 77 + call, outlier_frac=1e-3)
     x = O.synth_acts(1, K, 5 + call)
     ks = K // world

@@ -47,6 +47,7 @@ SIGNATURES = {
     "s12_gemm_async": (_i, [C.POINTER(S12Tensor), _vp, _i, _vp, _i, _i, _vp]),
     "s12_gemm_multi_async": (_i, [C.POINTER(S12Tensor), _i, _vp, _i, C.POINTER(_vp), C.POINTER(_i), _i, _vp]),
     "s12_gemm_noalloc_async": (_i, [C.POINTER(S12Tensor), _vp, _i, _vp, _i, _i, _vp]),
+    "s12_init": (_i, []),
     "s12_set_dependent_launch": (_i, [_i]),
     "s12_last_error": (C.c_char_p, []),
     "s12_version": (_i, []),
@@ -77,6 +78,8 @@ SIGNATURES = {
     "launch_store_kv_batch": (_i, [_vp] * 7 + [_i, _i, _i, _i, _i, _vp]),
     "launch_attention_all_heads": (_i, [_vp] * 6 + [_i, _i, _i, _i, _i, C.c_float, _vp]),
     "launch_attention_all_heads_batch": (_i, [_vp] * 7 + [_i, _i, _i, _i, C.c_float, _i, _i, _vp]),
+    "launch_flash_attention": (_i, [_vp] * 6 + [_i, _i, _i, _i, _i, C.c_float, _vp]),
+    "launch_flash_attention_batch": (_i, [_vp] * 7 + [_i, _i, _i, _i, C.c_float, _i, _i, _vp]),
     "s12_store_kv_batch": (_i, [_vp] * 7 + [_i, _i, C.c_longlong, _i, _vp]),
     "s12_rope_store_kv_batch": (_i, [_vp] * 8 + [_i, _i, _i, C.c_longlong, C.c_float, _i, _vp]),
     "s12_comm_handle_bytes": (_i, []),
@@ -86,6 +89,8 @@ SIGNATURES = {
     "s12_allreduce_f32_async": (_i, [_vp, _vp, _vp, _i, _vp]),
     "s12_allreduce_f32_emulated_async": (_i, [C.POINTER(_vp), _i, C.POINTER(_vp), C.POINTER(_vp), _i, _vp]),
     "s12_gemv_allreduce_async": (_i, [_vp, C.POINTER(S12Tensor), _vp, _vp, _vp]),
+    "s12_comm_set_wait_limit_ms": (_i, [_vp, _i]),
+    "s12_comm_reset": (_i, [_vp]),
     "s12_comm_destroy": (_i, [_vp]),
 }
 

@@ -108,7 +108,7 @@ allreduce_ll_kernel(const __grid_constant__ AllReduceParams P)
                 if ((unsigned int)(word >> 32) == token || gave_up) break;
                 const unsigned long long now = global_time_ns();
                 if (t0 == 0) t0 = now;
-                if (now - t0 > kPeerWaitLimitNs) { atomicOr(R.status, 0x8000u); gave_up = true; }   // the peer never arrived
+                if (now - t0 > R.wait_ns) { atomicOr(R.status, 0x8000u); gave_up = true; }   // the peer never arrived
             }
             acc += __uint_as_float((unsigned int)word);
         }
@@ -131,6 +131,7 @@ struct S12Comm {
     char* peer_base[s12::kCommMaxWorld] = {};  // every rank's allocation as mapped in this process
     bool opened[s12::kCommMaxWorld] = {};      // mapped through an IPC handle (must be closed)
     unsigned int* calls = nullptr;             // [0] calls completed, [1] CTAs done in the running call
+    unsigned long long wait_ns = s12::kPeerWaitLimitNs;   // bound of a wait for a peer
     bool connected = false;
 };
 
@@ -216,6 +217,7 @@ static int fill_rank(const S12Comm* c, s12::CommRank& R)
     }
     R.calls = c->calls;
     R.status = s12::device_status_word();
+    R.wait_ns = c->wait_ns;
     R.rank = c->rank;
     return R.status ? S12_OK : S12_ERR_CUDA;
 }
@@ -242,10 +244,8 @@ int s12_allreduce_f32_async(S12Comm* c, const void* in, void* out, int n, void* 
     if (fill_rank(c, P.r[0])) return fail(S12_ERR_CUDA, "%s: no status word", who);
     P.in[0] = (const float*)in; P.out[0] = (float*)out;
     P.world = c->world; P.capacity = c->capacity; P.n = n;
-    const char* e = getenv("S12_COMM_EARLY");                     // tuning knob, default on
-    P.early_trigger = e ? atoi(e) : 1;
-    const char* ll = getenv("S12_COMM_LL");                       // tuning knob, default on
-    if (n <= kCommLLMax && (!ll || atoi(ll))) {
+    P.early_trigger = env_knob("S12_COMM_EARLY", 1);              // tuning knobs, default on
+    if (n <= kCommLLMax && env_knob("S12_COMM_LL", 1)) {
         int ctas = (n + 1023) / 1024;
         ctas = ctas > 16 ? 16 : ctas;
         return launch(allreduce_ll_kernel, dim3(ctas, 1), dim3(256), 0, stream, who, P);
@@ -269,8 +269,7 @@ int s12_allreduce_f32_emulated_async(S12Comm* const* comms, int world, const voi
         P.in[r] = (const float*)ins[r]; P.out[r] = (float*)outs[r];
     }
     P.world = world; P.capacity = comms[0]->capacity; P.n = n;
-    const char* ll = getenv("S12_COMM_LL");
-    const bool small = n <= kCommLLMax && (!ll || atoi(ll));
+    const bool small = n <= kCommLLMax && env_knob("S12_COMM_LL", 1);
     const int ctas = small ? std::min(16, (n + 1023) / 1024) : comm_ctas(n);
     const int threads = small ? 256 : kCommThreads;
     const void* kern = small ? (const void*)allreduce_ll_kernel : (const void*)allreduce_kernel;
@@ -282,6 +281,26 @@ int s12_allreduce_f32_emulated_async(S12Comm* const* comms, int world, const voi
         return fail(S12_ERR_TOO_LARGE, "%s: %d x %d CTAs cannot be resident together", who, ctas, world);
     void* args[1] = {&P};
     return check_cuda(cudaLaunchCooperativeKernel(kern, dim3(ctas, world), dim3(threads), args, 0, (cudaStream_t)stream), who);
+}
+
+int s12_comm_set_wait_limit_ms(S12Comm* c, int ms)
+{
+    if (!c || ms < 1) return s12::fail(S12_ERR_BAD_ARG, "s12_comm_set_wait_limit_ms: need a communicator and ms >= 1");
+    const int old = (int)std::min<unsigned long long>(c->wait_ns / 1000000ull, 0x7FFFFFFFull);
+    c->wait_ns = (unsigned long long)ms * 1000000ull;
+    return old;
+}
+
+int s12_comm_reset(S12Comm* c)
+{
+    using namespace s12;
+    const char* who = "s12_comm_reset";
+    if (!c) return fail(S12_ERR_BAD_ARG, "%s: null communicator", who);
+    int rc = check_cuda(cudaDeviceSynchronize(), who);
+    if (!rc) rc = check_cuda(cudaMemset(c->base, 0, c->recv_bytes + c->flag_bytes + c->ll_bytes), who);
+    if (!rc) rc = check_cuda(cudaMemset(c->calls, 0, 2 * sizeof(unsigned int)), who);
+    if (!rc) rc = check_cuda(cudaDeviceSynchronize(), who);
+    return rc;
 }
 
 int s12_comm_destroy(S12Comm* c)

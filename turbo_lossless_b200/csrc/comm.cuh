@@ -32,6 +32,7 @@ struct CommRank {
     unsigned long long* ll[kCommMaxWorld];   // every rank's small-message area: 8-byte words {value bits, token}
     unsigned int* calls;                     // local: [0] collective calls completed, [1] CTAs of the running call that are done
     unsigned int* status;                    // local status word (bit 0x8000: a wait gave up)
+    unsigned long long wait_ns;              // how long a wait for a peer may last (s12_comm_set_wait_limit_ms)
     int rank;
 };
 
@@ -75,7 +76,7 @@ __device__ __forceinline__ void comm_signal_and_wait(const CommRank& R, int worl
         while ((int)(ld_acquire_sys(f) - token) < 0) {
             const unsigned long long now = global_time_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > kPeerWaitLimitNs) { atomicOr(R.status, 0x8000u); break; }    // the peer never arrived
+            if (now - t0 > R.wait_ns) { atomicOr(R.status, 0x8000u); break; }    // the peer never arrived
             __nanosleep(200);
         }
     }

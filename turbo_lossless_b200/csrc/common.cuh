@@ -17,6 +17,13 @@ bool dependent_launch_enabled();
 constexpr int kMaxGemmTensors = 8;
 int  sm_count();                                    // SMs of the current device (cached)
 unsigned int* device_status_word();                 // per-device status word (device pointer)
+bool tuning_enabled();                              // S12_TUNE=1 was set when the library was first used
+int  env_knob(const char* name, int dflt);          // a tuning knob's value; dflt unless tuning is enabled
+// gemm_tc.cu: per-device set-up of the tensor-core GEMM (workspace, kernel attributes), the status word of
+// the allocation-free entry point, and the hand-over counters of the stream-K workspace
+int  gemm_tc_prepare(const char* who);
+int  gemm_noalloc_status_read_clear(unsigned int* out);
+int  gemm_tc_reset_counters();
 
 // Launches `kernel` on `stream`; when dependent launch is enabled the launch
 // carries the programmatic-stream-serialization attribute so that the kernel

@@ -75,18 +75,6 @@ constexpr int kGemmThreads = (kFirstEpiWarp + 4) * 32;
 constexpr int kGroupThreads = kDecodeWarps * 32 / kDecodeGroups;            // 128
 static_assert(kGroupThreads == kTM, "one decode thread per tile row");
 
-#ifdef S12_GEMM_TRACE
-// Development aid: cycle stamps of the pipeline roles of CTA 0, per raw stage.
-__device__ long long g_gtrace[64][48];
-#define GT(i, slot) do { if (blockIdx.x == 0 && (i) < 64) g_gtrace[(i)][(slot)] = clock64(); } while (0)
-// wall-clock (ns) stamps of kernel phases, per CTA; row 160 = reduce kernel (min start, max end)
-__device__ unsigned long long g_gphase[161][12];
-__device__ __forceinline__ unsigned long long gt_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define GP(slot) do { g_gphase[blockIdx.x][(slot)] = gt_now(); } while (0)
-#else
-#define GT(i, slot) do { } while (0)
-#define GP(slot) do { } while (0)
-#endif
 
 
 struct GemmTensor {
@@ -459,7 +447,6 @@ __device__ __noinline__ void cluster_reduce(const GemmParams& P, uint8_t* smem, 
     if (warp >= kFirstDecodeWarp) {
         mbar_wait(b_accfull, 0, P.status, 0x2000u, s_abort);      // all MMAs of this CTA have finished
         tc_fence_after();
-        if (warp == kFirstEpiWarp && lane == 0) GP(6);
         const int q = warp & 3, mrow = q * 32 + lane;
         const int team = warp >= kFirstEpiWarp ? 0 : 1 + (warp - kFirstDecodeWarp) / 4;
         for (int c = team; c < nch; c += kDrainTeams) {
@@ -471,9 +458,7 @@ __device__ __noinline__ void cluster_reduce(const GemmParams& P, uint8_t* smem, 
             for (int j = 0; j < 32; j++) dst[j * kTileRows] = __uint_as_float(v[j]);
         }
     }
-    if (warp == kFirstEpiWarp && lane == 0) GP(7);
     cluster_sync_all();                                           // every CTA of the cluster has staged its partial tile
-    if (warp == kFirstEpiWarp && lane == 0) GP(8);
     const uint32_t rank = cluster_ctarank();
     grid_dependency_wait();                                       // the output buffer may still be in use
     const int mtg = tile0 / P.n_ntiles, nt = tile0 - mtg * P.n_ntiles;
@@ -502,9 +487,7 @@ __device__ __noinline__ void cluster_reduce(const GemmParams& P, uint8_t* smem, 
             if (m + 3 < T.M) dst[3] = acc.w;
         }
     }
-    if (warp == kFirstEpiWarp && lane == 0) GP(9);
     cluster_sync_all();                                           // nobody reads this CTA's shared memory any more
-    if (warp == kFirstEpiWarp && lane == 0) GP(10);
 }
 
 // When the accumulator cannot be double buffered (BN > 192) the MMAs of the next
@@ -540,7 +523,6 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     const int cs = P.cluster;                                    // CTAs of the cluster that share this CTA's tile
 
     if (threadIdx.x == 0) {
-        GP(0);
         s_abort = 0;
         for (int i = 0; i < kRawStages; i++) { mbar_init(b_rawfull + 8 * i, 1); mbar_init(b_rawempty + 8 * i, kDecodeWarps); }
         for (int i = 0; i < kSub; i++) { mbar_init(b_full + 8 * i, kDecodeWarps / kDecodeGroups + 1); mbar_init(b_free + 8 * i, 1); }
@@ -560,7 +542,6 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     grid_launch_dependents();
-    if (threadIdx.x == 0) GP(1);
 
     // The schedule counts raw stages ("big blocks" of kBigK columns); a tile has
     // KB of them, the last one zero-filled by TMA past column K.
@@ -579,7 +560,6 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             for (int it = rg.lo; it < rg.hi; it++) {
                 if (wr > 0) mbar_wait(b_rawempty + 8 * sr, (wr - 1) & 1, P.status, 0x10u, &s_abort);
                 const uint32_t bar = b_rawfull + 8 * sr;
-                GT(it - rg.lo, 0);
                 mbar_arrive_expect_tx(bar, kRawBytes);
                 const uint32_t rdst = smem_addr(raw + sr * kRawBytes);
                 const int y = tr.mt * kTileRows;
@@ -601,7 +581,6 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
 #pragma unroll
                 for (int sub = 0; sub < kSub; sub++) {
                     if (it > rg.lo) mbar_wait(b_free + 8 * sub, (uint32_t)(it - rg.lo - 1) & 1, P.status, 0x20u, &s_abort);
-                    GT(it - rg.lo, 1 + sub);
                     mbar_arrive_expect_tx(b_full + 8 * sub, xbytes);
                     tma_load_2d(smem_addr(Xbuf + (size_t)sub * xbytes), &map_x, kb * kBigK + sub * kTK, xr0 + nt * BN, b_full + 8 * sub);
                 }
@@ -633,7 +612,6 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
 #pragma unroll
                 for (int sub = 0; sub < kSub; sub++) {
                     if (!ready) mbar_wait(b_full + 8 * sub, wa & 1, P.status, 0x80u, &s_abort);
-                    GT(it - rg.lo, 5 + sub);
                     tc_fence_after();
                     // look at the next stage now: the test's latency hides behind the MMA issue
                     ready = sub + 1 < kSub ? mbar_test(b_full + 8 * (sub + 1), wa & 1) : mbar_test(b_full, (wa + 1) & 1);
@@ -644,9 +622,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
                         for (int k = 0; k < kTK / 16; k++)       // 16 k = 8 columns of packed bf16 pairs
                             umma_bf16_ts(d_tmem, a_tmem + (uint32_t)(8 * k), bd + (uint64_t)(2 * k), idesc,
                                          k == 0 ? accumulate : 1u);
-                        GT(it - rg.lo, 33 + sub);
                         umma_commit(b_free + 8 * sub);           // A stage and activation stage are free when these finish
-                        GT(it - rg.lo, 37 + sub);
                     }
                     accumulate = 1;
                 }
@@ -673,27 +649,20 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
         const uint32_t a_dst = tmem_base + ((uint32_t)((t >> 5) * 32) << 16) + kATmemBase + (uint32_t)gi * kATmemCols;
         for (int it = rg.lo; it < rg.hi; it++) {
             mbar_wait(b_rawfull + 8 * sr, wr & 1, P.status, 0x200u, &s_abort);
-            if (t == 0) GT(it - rg.lo, 13 + 5 * gi);
-            if (dt == 0 && it == rg.lo) GP(2);
             const GemmTensor& T = P.t[tr.ti];
             uint32_t v[32];
             if (P.neg_base) decode_row<1>(raw + sr * kRawBytes, t, gi, T.base2, v);
             else decode_row<0>(raw + sr * kRawBytes, t, gi, T.base2, v);
             __syncwarp();
-            if (t == 0) GT(it - rg.lo, 14 + 5 * gi);
             if (lane == 0) mbar_arrive(b_rawempty + 8 * sr);      // this warp has read its share of the stage
             esc_apply(esc, T, kb * kBigK + gi * kTK, v);
-            if (t == 0) GT(it - rg.lo, 15 + 5 * gi);
             if (wo > 0) mbar_wait(b_free + 8 * gi, (wo - 1) & 1, P.status, 0x400u, &s_abort);
-            if (t == 0) GT(it - rg.lo, 16 + 5 * gi);
             tc_fence_after();
             tmem_st32(a_dst, v);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(b_full + 8 * gi);
-            if (t == 0) GT(it - rg.lo, 17 + 5 * gi);
-            if (dt == 0 && it == rg.hi - 1) GP(3);
             if (kb + 1 == KB || it + 1 == rg.hi) {                // last raw stage of a tile segment
                 if (!two_acc && cs <= 1) {
                     mbar_wait(b_accfull, (uint32_t)nacc & 1, P.status, 0x1000u, &s_abort);
@@ -748,7 +717,6 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             it = seg_end;
             tile++;
         }
-        if (warp == kFirstEpiWarp && lane == 0) GP(4);
     }
 
     if (cs > 1) cluster_reduce(P, smem, tmem_base, b_accfull, &s_abort);
@@ -758,7 +726,6 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
-    if (threadIdx.x == 0) GP(5);
 }
 
 // ----------------------------------------------------------------------------
@@ -801,30 +768,34 @@ static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, u
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Per-device workspace for partial accumulators (grow-only, allocated on first
-// use or when a larger one is needed), followed by the hand-over counters of
-// the slots, which start at zero and are left at zero by every launch.
+// Per-device workspace for the partial accumulators of the stream-K schedule: one slot of
+// 256 x 128 floats per SM (the largest launch), followed by the hand-over counters of the
+// slots, which start at zero and are left at zero by every launch.  Allocated once per
+// device, by s12_init() or by the first GEMM call on the device (cudaMalloc synchronises:
+// callers that need every call to be asynchronous run s12_init() first).
+//
+// All GEMM launches of a device share this workspace, so two launches that may overlap on
+// the GPU (different streams) would mix their partial tiles: the GEMM entry points must be
+// serialised per device by the caller (one stream, or events between streams).
 constexpr size_t kFlagBytes = 4096;                              // room for 1024 CTAs
 struct Scratch { float* ws = nullptr; unsigned int* flags = nullptr; size_t ws_bytes = 0; };
 static Scratch g_scratch[64];
 static std::mutex g_scratch_mu;
 
-static int get_scratch(size_t ws_bytes, Scratch& out, const char* who)
+static int get_scratch(Scratch& out, const char* who)
 {
     int dev = 0;
     cudaGetDevice(&dev);
     dev = (dev < 0 || dev >= 64) ? 0 : dev;
+    const size_t ws_bytes = (size_t)sm_count() * 256 * kTileRows * sizeof(float);
     std::lock_guard<std::mutex> lk(g_scratch_mu);
     Scratch& s = g_scratch[dev];
-    if (s.ws_bytes < ws_bytes) {
-        cudaDeviceSynchronize();
-        if (s.ws) cudaFree(s.ws);
-        s.ws = nullptr; s.ws_bytes = 0;
+    if (!s.ws) {
         int rc = check_cuda(cudaMalloc(&s.ws, ws_bytes + kFlagBytes), who);
-        if (rc) return rc;
+        if (rc) { s.ws = nullptr; return rc; }
         s.flags = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(s.ws) + ws_bytes);
         rc = check_cuda(cudaMemset(s.flags, 0, kFlagBytes), who);
-        if (rc) return rc;
+        if (rc) { cudaFree(s.ws); s.ws = nullptr; return rc; }
         s.ws_bytes = ws_bytes;
     }
     out = s;
@@ -928,12 +899,6 @@ static int cluster_fit(int s)
     return cache[dev][s] - 1;
 }
 
-static int gemm_env_int(const char* name, int dflt)
-{
-    const char* e = getenv(name);
-    return (e && *e) ? atoi(e) : dflt;
-}
-
 // Picks how the iteration space is cut (P.split) and the number of CTAs, at most
 // max_grid, by a small cost model in microseconds whose constants were measured
 // on this kernel: a raw stage takes ~1.25 us, every tile segment of a CTA costs
@@ -949,7 +914,7 @@ static int choose_schedule(GemmParams& P, int max_grid)
     int best_split = 0;
     double per = (double)T / best_grid;
     double best = per * tb + seg * (1.0 + per / P.KB) + (best_grid > 1 ? fixup(2.0 * best_grid) : 0.0);
-    const int forced = gemm_env_int("S12_GEMM_SPLIT", -1);           // tuning knob: -1 model, 0 stream-K, n parts per tile
+    const int forced = env_knob("S12_GEMM_SPLIT", -1);           // tuning knob: -1 model, 0 stream-K, n parts per tile
     // Fixed parts: measured, only whole tiles in a single round beat stream-K (CTAs that switch tiles
     // all at once collide in their drains; staggered stream-K ranges do not).  Other values of the
     // knob remain for experiments.
@@ -966,11 +931,12 @@ static int choose_schedule(GemmParams& P, int max_grid)
     P.cluster = 0;
     // Few tiles (at most half as many as SMs): cut every tile into s parts that run as one cluster and add
     // up on chip.  No workspace, no second kernel, and no CTA ever switches tiles.
-    const int cforced = gemm_env_int("S12_GEMM_CLUSTER", -1);        // tuning knob: -1 auto, 0 off, n CTAs per tile
+    const int cforced = env_knob("S12_GEMM_CLUSTER", -1);        // tuning knob: -1 auto, 0 off, n CTAs per tile
     const int sms = sm_count();
-    if (cforced != 0 && forced < 0 && tiles * 2 <= sms) {
-        int s = (int)std::min<long long>(std::min<long long>(sms / tiles, P.KB / 2), 8);
-        if (cforced > 0) s = std::min(cforced, std::min(P.KB, 8));
+    const int cta_cap = std::min(sms, max_grid);                     // callers with a small workspace pass fewer CTAs than SMs
+    if (cforced != 0 && forced < 0 && tiles * 2 <= cta_cap) {
+        int s = (int)std::min<long long>(std::min<long long>(cta_cap / tiles, P.KB / 2), 8);
+        if (cforced > 0) s = (int)std::min<long long>(std::min(cforced, std::min(P.KB, 8)), std::max<long long>(1, cta_cap / tiles));
         const size_t ring = (size_t)kRawStages * kRawBytes + (size_t)kXStages * P.BN * 128;
         const int nch = (P.BN + 31) / 32;
         if ((size_t)nch * 32 * kTileRows * 4 > ring) s = 0;           // a CTA stages its whole partial tile in the rings
@@ -990,20 +956,41 @@ int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_st
     int rc = gemm_fill(P, maps, mx, w, nt, act, act_stride, outs, out_strides, B, who, act_row0);
     if (rc) return rc;
     P.status = device_status_word();
+    if (!P.status) return fail(S12_ERR_CUDA, "%s: no device status word", who);
 
     const long long T = (long long)P.n_mtiles * P.n_ntiles * P.KB;
     if (T >= (1ll << 31)) return fail(S12_ERR_TOO_LARGE, "%s: problem too large for the tile schedule", who);
     const int sms = sm_count();
     rc = ensure_smem_attr(who);
     if (rc) return rc;
-    const int grid = choose_schedule(P, sms);
+    const int grid = choose_schedule(P, std::max(1, std::min(sms, env_knob("S12_GEMM_MAXGRID", sms))));   // knob: tests cap the CTA count
     Scratch sc;
-    rc = get_scratch((size_t)sms * 256 * kTileRows * sizeof(float), sc, who);      // one slot per CTA, largest launch
+    rc = get_scratch(sc, who);                                    // one slot per CTA, largest launch
     if (rc) return rc;
     P.ws = sc.ws;
     P.flags = sc.flags;
     const size_t smem = gemm_smem_bytes(P.BN);
     return launch_clustered(gemm_tc_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, who, P.cluster, maps, mx, P);
+}
+
+int gemm_tc_prepare(const char* who)
+{
+    if (!encode_fn()) return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled unavailable", who);
+    int rc = ensure_smem_attr(who);
+    if (rc) return rc;
+    Scratch sc;
+    return get_scratch(sc, who);
+}
+
+// Zeroes the hand-over counters of the current device's workspace (after a launch that gave up).
+int gemm_tc_reset_counters()
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = (dev < 0 || dev >= 64) ? 0 : dev;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    if (!g_scratch[dev].flags) return S12_OK;
+    return check_cuda(cudaMemset(g_scratch[dev].flags, 0, kFlagBytes), "s12_device_status");
 }
 
 int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
@@ -1068,6 +1055,30 @@ static int noalloc_setup(NoAllocState& out, const char* who)
         st.ws = ws; st.status = status; st.flags = flags; st.ready = true;
     }
     out = st;
+    return S12_OK;
+}
+
+// Reads and clears the status word of the allocation-free entry point on the current device (0 when that
+// entry point has not been used there) and, when it was non-zero, its hand-over counters.  Called by
+// s12_device_status() after it has synchronised the device.
+int gemm_noalloc_status_read_clear(unsigned int* out)
+{
+    *out = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return S12_OK;
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    const NoAllocState& st = g_noalloc[dev];
+    if (!st.ready) return S12_OK;
+    unsigned int v = 0;
+    int rc = check_cuda(cudaMemcpy(&v, st.status, sizeof v, cudaMemcpyDeviceToHost), "s12_device_status");
+    if (rc) return rc;
+    if (v) {
+        rc = check_cuda(cudaMemset(st.status, 0, sizeof v), "s12_device_status");
+        if (!rc) rc = check_cuda(cudaMemset(st.flags, 0, sizeof(unsigned int) * 256), "s12_device_status");
+        if (rc) return rc;
+    }
+    *out = v;
     return S12_OK;
 }
 

@@ -28,7 +28,6 @@
 // split12_matvec_v2* (decompress_v2.hip:148-523) and, through the escape-table
 // entry points, split12_matvec_batch4/8 (decompress_v2.hip:573-856).
 #include "common.cuh"
-#include <cstdlib>
 
 namespace s12 {
 
@@ -371,18 +370,12 @@ gemv_generic_kernel(const __grid_constant__ GemvParams P, int mode)
 int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* outs, int mode,
                     void* stream, const char* who, int* rc_out, const S12Comm* comm);
 
-static int env_int(const char* name, int dflt)
-{
-    const char* e = getenv(name);
-    return (e && *e) ? atoi(e) : dflt;
-}
-
 template <int kMode, int kNB>
 static int launch_gemv_warps(const GemvParams& P, int rg_total, void* stream)
 {
     // More warps per row group when there are few row groups, so that every SM
     // keeps enough loads in flight; S12_GEMV_WARPS overrides for tuning.
-    static const int forced = env_int("S12_GEMV_WARPS", 0);
+    const int forced = env_knob("S12_GEMV_WARPS", 0);
     const int sms = sm_count();
     int warps = forced ? forced : (rg_total >= 6 * sms ? 4 : 8);
     if (kNB == 2) warps = 4;
@@ -406,7 +399,8 @@ struct GemvCall {
     const S12Comm* comm;                // tensor-parallel call: the result is summed over the communicator's ranks
 };
 
-int gemv_dispatch(const GemvCall& c, void* stream)
+// `reduced` is set when the launch already summed the result over the communicator's ranks.
+static int gemv_dispatch_body(const GemvCall& c, void* stream, bool& reduced)
 {
     const char* who = c.who;
     if (!c.w || c.nt < 1 || c.nt > S12_MAX_MULTI) return fail(S12_ERR_BAD_ARG, "%s: bad tensor list", who);
@@ -479,15 +473,24 @@ int gemv_dispatch(const GemvCall& c, void* stream)
         void* outs[S12_MAX_MULTI];
         for (int i = 0; i < c.nt; i++) outs[i] = c.o[i];
         int used = gemv_stream_try(c.w, c.nt, c.x[0], outs, mode, stream, who, &rc, c.comm);
-        if (used != 0) return rc;
-        rc = S12_GEMV_MODE(0);
-        // tensor-parallel call that the streaming kernel did not take: plain GEMV, then the all-reduce kernel
-        if (rc == S12_OK && c.comm) rc = s12_allreduce_f32_async(const_cast<S12Comm*>(c.comm), outs[0], outs[0], c.w[0].M, stream);
-        return rc;
+        if (used != 0) { reduced = c.comm != nullptr; return rc; }
+        return S12_GEMV_MODE(0);
     }
     if (c.B <= 8) return S12_GEMV_MODE(1);
     return S12_GEMV_MODE(2);
 #undef S12_GEMV_MODE
+}
+
+// Every path of a tensor-parallel call ends in the sum over ranks: the streaming kernel does it itself;
+// the register-pipelined kernel, the general path (K not a multiple of 32, unaligned pointers) and K == 0
+// are followed by the all-reduce kernel.
+int gemv_dispatch(const GemvCall& c, void* stream)
+{
+    bool reduced = false;
+    int rc = gemv_dispatch_body(c, stream, reduced);
+    if (rc == S12_OK && c.comm && !reduced)
+        rc = s12_allreduce_f32_async(const_cast<S12Comm*>(c.comm), c.o[0], c.o[0], c.w[0].M, stream);
+    return rc;
 }
 
 // Strided batched form used by s12_gemv_batched_async and the GEMM dispatcher.

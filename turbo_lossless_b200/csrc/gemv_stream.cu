@@ -44,7 +44,7 @@
 //     partials of its own rows (comm.cuh).
 //   * All waits are bounded (common.cuh).
 #include "comm.cuh"
-#include <cstdlib>
+#include <mutex>
 
 namespace s12 {
 
@@ -94,27 +94,10 @@ struct StreamParams {
     // own rows (protocol in comm.cuh).  tp_world == 0: plain store.
     CommRank tp;
     int tp_world, tp_cap;
-#ifdef S12_TRACE
-    int trace_slot;
-#endif
 };
 
 struct BlockRef { int ti; int r0; };
 
-#ifdef S12_TRACE
-// Development aid: per-CTA timestamps (ns) of kernel phases.
-__device__ unsigned long long g_trace[4][148 * 8];
-int g_trace_slot_host = 0;
-__device__ __forceinline__ unsigned long long now_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define S12_STAMP(slot) do { if (lane == 0 && blockIdx.x < 148) g_trace[P.trace_slot & 3][blockIdx.x * 8 + (slot)] = now_ns(); } while (0)
-#else
-#define S12_STAMP(slot) do { } while (0)
-#endif
 
 __device__ __forceinline__ BlockRef locate_block(const StreamParams& P, int blk)
 {
@@ -149,7 +132,6 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
     __shared__ int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) s_abort = 0;
-    if (warp == 0) S12_STAMP(0);
     if (threadIdx.x < kMaxDepth) {
         mbar_init(bar_full + 8 * threadIdx.x, 1);
         mbar_init(bar_empty + 8 * threadIdx.x, kGroupWarps);
@@ -218,9 +200,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             }
             if (++s == depth) { s = 0; wrap++; }
             if (++kt == P.tpr) { kt = 0; blk++; if (blk < b1) br = locate_block(P, blk); }
-            if (i == 0) S12_STAMP(1);
         }
-        S12_STAMP(6);
         return;
     }
 
@@ -245,7 +225,6 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             xperm[xchunk_base(c) + (uu & ~15) + pos] = pv;
         }
         named_bar_sync(1, kConsumers * 32);
-        if (warp == 0) S12_STAMP(2);
 
         // two groups of eight warps work on alternate tiles; inside a group warp
         // wi takes columns [wi*128, wi*128+128) of every segment
@@ -282,7 +261,6 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         for (int i = grp; i < ntiles; i += kGroups) {
             if (jb != jb_loaded) { base2 = P.t[locate_block(P, b0 + jb).ti].base2; jb_loaded = jb; }
             mbar_wait(bar_full + 8 * s, wrap & 1, P.status, 2u, &s_abort);
-            if (warp == 0 && i == 0) S12_STAMP(3);
             const uint8_t* st = ring + (size_t)s * kStageBytes;
             const uint4 af = *reinterpret_cast<const uint4*>(st + offA + first);
             const uint4 as = *reinterpret_cast<const uint4*>(st + offA + second);
@@ -344,7 +322,6 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             s += kGroups;
             if (s >= depth) { s -= depth; wrap++; }
         }
-        if (warp == 0) S12_STAMP(4);
         return;
     }
 
@@ -421,13 +398,6 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         named_bar_sync(5, kEpiThreads);
         if (tid == 0) comm_retire(P.tp, tp_token, gridDim.x);
     }
-    if (e == 0) S12_STAMP(5);
-}
-
-static int env_int2(const char* name, int dflt)
-{
-    const char* e = getenv(name);
-    return (e && *e) ? atoi(e) : dflt;
 }
 
 // Returns 1 and launches when the streaming kernel applies; 0 when the caller
@@ -435,9 +405,9 @@ static int env_int2(const char* name, int dflt)
 int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* outs, int mode,
                     void* stream, const char* who, int* rc_out, const S12Comm* comm)
 {
-    const int impl = env_int2("S12_GEMV_IMPL", 1);              // 0: never, 1: auto (tuning/test knobs)
-    const int force_r = env_int2("S12_GEMV_R", 0);
-    const int force_depth = env_int2("S12_GEMV_DEPTH", 0);
+    const int impl = env_knob("S12_GEMV_IMPL", 1);              // 0: never, 1: auto (tuning/test knobs)
+    const int force_r = env_knob("S12_GEMV_R", 0);
+    const int force_depth = env_knob("S12_GEMV_DEPTH", 0);
     if (!impl) return 0;
     const int K = w[0].K;
     if (K % 32 != 0 || K < 128) return 0;
@@ -473,28 +443,28 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
         P.tp_world = world; P.tp_cap = cap;
     }
     P.status = device_status_word();
+    if (!P.status) { *rc_out = fail(S12_ERR_CUDA, "%s: no device status word", who); return -1; }
     P.mul.m128 = 128u; P.mul.m8 = 8u; P.mul.hi24 = 1u << 24;
-#ifdef S12_TRACE
-    P.trace_slot = g_trace_slot_host;
-#endif
 
     // Shape of the launch: consumer groups per CTA and CTAs per SM (tuning knobs
     // S12_GEMV_GROUPS / S12_GEMV_CTAS).  Default: one group, two CTAs per SM.
-    int groups = env_int2("S12_GEMV_GROUPS", 1);
+    int groups = env_knob("S12_GEMV_GROUPS", 1);
     groups = groups == 2 ? 2 : 1;
-    int ctas = groups == 2 ? 1 : env_int2("S12_GEMV_CTAS", 2);
+    int ctas = groups == 2 ? 1 : env_knob("S12_GEMV_CTAS", 2);
     ctas = ctas == 1 ? 1 : 2;
     const int consumers = groups * kGroupWarps;
     const size_t fixed = (size_t)xunits_total(P.tpr * Q) * 16 + (size_t)kRedSlots * consumers * 16 * sizeof(float) +
                          8 * (2 * kMaxDepth + 2 * kRedSlots);
+    // device limits, queried once (all devices of a process are taken to be the same part)
     static int optin = 0, static_smem = 0;
-    if (!optin) {
+    static std::once_flag limits_once;
+    std::call_once(limits_once, [] {
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         cudaFuncAttributes fa;
         static_smem = cudaFuncGetAttributes(&fa, gemv_stream_kernel<0, 1, true>) == cudaSuccess ? (int)fa.sharedSizeBytes : 1024;
-    }
+    });
     // dynamic shared memory one CTA may use: everything, or what lets two CTAs (1 KB reserved each) share an SM
     const int per_cta = (ctas == 2 ? (optin + 1024) / 2 - 1024 : optin) - static_smem;
     if ((size_t)per_cta < fixed + 2 * (size_t)kStageBytes) {
@@ -515,7 +485,7 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     const size_t smem = fixed + (size_t)depth * kStageBytes;
 
     typedef void (*Kern)(const StreamParams);
-    const int swap = env_int2("S12_GEMV_SWAP", 0) ? 1 : 0;   // 0: plain load order (fewer instructions, measured faster)
+    const int swap = env_knob("S12_GEMV_SWAP", 0) ? 1 : 0;   // 0: plain load order (fewer instructions, measured faster)
     static const Kern table[2][2][3] = {
         {{gemv_stream_kernel<0, 1, false>, gemv_stream_kernel<1, 1, false>, gemv_stream_kernel<2, 1, false>},
          {gemv_stream_kernel<0, 2, false>, gemv_stream_kernel<1, 2, false>, gemv_stream_kernel<2, 2, false>}},
@@ -523,13 +493,17 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
          {gemv_stream_kernel<0, 2, true>, gemv_stream_kernel<1, 2, true>, gemv_stream_kernel<2, 2, true>}}};
     Kern kern = table[swap][groups - 1][mode];
     static bool attr_set[64][4][3];
+    static std::mutex attr_mu;
     int dev = 0;
     cudaGetDevice(&dev);
     dev = (dev < 0 || dev >= 64) ? 0 : dev;
-    if (!attr_set[dev][swap * 2 + groups - 1][mode]) {
-        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - static_smem), who);
-        if (rc) { *rc_out = rc; return -1; }
-        attr_set[dev][swap * 2 + groups - 1][mode] = true;
+    {
+        std::lock_guard<std::mutex> lk(attr_mu);
+        if (!attr_set[dev][swap * 2 + groups - 1][mode]) {
+            int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - static_smem), who);
+            if (rc) { *rc_out = rc; return -1; }
+            attr_set[dev][swap * 2 + groups - 1][mode] = true;
+        }
     }
     const int slots = sms * ctas;
     const int grid = blocks < slots ? blocks : slots;

@@ -18,6 +18,7 @@ namespace s12 {
 __global__ void __launch_bounds__(256)
 hist_kernel(const uint16_t* __restrict__ w, int64_t n, unsigned long long* __restrict__ hist)
 {
+    grid_dependency_wait();                    // inputs and outputs may belong to the predecessor kernel
     __shared__ unsigned int sh[256];
     sh[threadIdx.x] = 0;
     __syncthreads();
@@ -33,6 +34,7 @@ __global__ void __launch_bounds__(256)
 pack16_kernel(const uint16_t* __restrict__ w, int64_t num_chunks, int K, int base_exp,
               uint8_t* __restrict__ sm, uint8_t* __restrict__ gr, int32_t* __restrict__ row_off)
 {
+    grid_dependency_wait();
     const int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (c >= num_chunks) return;
     const uint4* src = reinterpret_cast<const uint4*>(w + c * 16);
@@ -60,6 +62,7 @@ __global__ void __launch_bounds__(256)
 pack2_kernel(const uint16_t* __restrict__ w, int64_t num_pairs, int K, int base_exp,
              uint8_t* __restrict__ sm, uint8_t* __restrict__ gr, int32_t* __restrict__ row_off)
 {
+    grid_dependency_wait();
     const int64_t pr = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (pr >= num_pairs) return;
     uint32_t gb = 0;
@@ -80,6 +83,7 @@ pack2_kernel(const uint16_t* __restrict__ w, int64_t num_pairs, int K, int base_
 __global__ void __launch_bounds__(1024)
 scan_kernel(int32_t* __restrict__ row_off, int M)
 {
+    grid_dependency_wait();                    // the per-row counts come from the pack kernel before
     __shared__ int warp_tot[32];
     __shared__ int carry_s;
     if (threadIdx.x == 0) carry_s = 0;
@@ -119,6 +123,7 @@ fill_kernel(const uint16_t* __restrict__ w, int M, int K, int base_exp,
             const int32_t* __restrict__ row_off, int32_t* __restrict__ cols,
             int16_t* __restrict__ correct, int16_t* __restrict__ wrong)
 {
+    grid_dependency_wait();                    // row_off comes from the scan kernel before
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= M) return;
     int pos = row_off[row];

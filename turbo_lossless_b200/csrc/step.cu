@@ -575,10 +575,16 @@ static int attention_launch(AttnParams& P, int max_len, int batch, void* stream,
     int nsplit = 1;
     const long long pairs = (long long)P.n_head_kv * batch;
     while (nsplit < 8 && pairs * nsplit * 2 <= sm_count() && max_len / (nsplit * 2) >= kAttnWarps) nsplit *= 2;
+    auto smem_for = [&](int ns) {
+        const int per = (max_len + ns - 1) / ns;
+        return ((size_t)(gqa + 2) * ((per + 3) & ~3) + (size_t)kAttnWarps * gqa * P.head_dim + 2 * gqa) * sizeof(float);
+    };
+    // long contexts: more slices (also with many sequences) until one slice's scores fit a CTA's shared memory
+    while (nsplit < 8 && smem_for(nsplit) > 200 * 1024) nsplit *= 2;
     P.nsplit = nsplit;
     const int per = (max_len + nsplit - 1) / nsplit;
     P.score_stride = (per + 3) & ~3;
-    const size_t smem = ((size_t)(gqa + 2) * P.score_stride + (size_t)kAttnWarps * gqa * P.head_dim + 2 * gqa) * sizeof(float);
+    const size_t smem = smem_for(nsplit);
     if (smem > 200 * 1024) return fail(S12_ERR_TOO_LARGE, "%s: seq_len %d needs more shared memory than one CTA has", who, max_len);
     typedef void (*Kern)(const AttnParams);
     static const Kern table[4][2] = {{attention_kernel<1, 1>, attention_kernel<1, 2>}, {attention_kernel<2, 1>, attention_kernel<2, 2>},
@@ -724,6 +730,23 @@ int launch_attention_all_heads_batch(const float* q, const int8_t* kv_k, const i
     P.q = q; P.kc = kv_k; P.vc = kv_v; P.sk = kv_scale_k; P.sv = kv_scale_v; P.out = output; P.positions = positions;
     P.n_head = n_head; P.n_head_kv = n_head_kv; P.head_dim = head_dim; P.kv_stride = kv_stride;
     return attention_launch(P, max_seq, batch_size, stream, "launch_attention_all_heads_batch");   // max_seq: largest position + 1
+}
+
+// The engine switches to these two names from position 1024 on (engine/inference.cpp:285,432,505,627); same
+// arguments as the two launchers above, same kernels here (they have no 1024-position limit).
+int launch_flash_attention(const float* q, const int8_t* k_cache, const int8_t* v_cache, const float* kv_scale_k,
+                           const float* kv_scale_v, int16_t* output, int n_head, int n_head_kv, int head_dim, int seq_len,
+                           int max_seq, float scale, void* stream)
+{
+    return launch_attention_all_heads(q, k_cache, v_cache, kv_scale_k, kv_scale_v, output, n_head, n_head_kv, head_dim, seq_len,
+                                      max_seq, scale, stream);
+}
+int launch_flash_attention_batch(const float* q, const int8_t* kv_k, const int8_t* kv_v, const float* kv_scale_k,
+                                 const float* kv_scale_v, int16_t* output, const int* positions, int n_head, int n_head_kv,
+                                 int head_dim, int max_seq, float scale, int batch_size, int kv_stride, void* stream)
+{
+    return launch_attention_all_heads_batch(q, kv_k, kv_v, kv_scale_k, kv_scale_v, output, positions, n_head, n_head_kv, head_dim,
+                                            max_seq, scale, batch_size, kv_stride, stream);
 }
 
 }  // extern "C"

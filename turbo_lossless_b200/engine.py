@@ -442,6 +442,10 @@ class Split12Engine:
                                                         scale, batch, kv_stride, _stream(stream)),
               "launch_attention_all_heads_batch")
 
+    def init(self) -> None:
+        """Per-device set-up ahead of the first call (s12_init): status word, GEMM workspace, kernel attributes."""
+        check(self.lib.s12_init(), "s12_init")
+
     def set_dependent_launch(self, enable: bool) -> bool:
         return bool(self.lib.s12_set_dependent_launch(1 if enable else 0))
 
@@ -505,6 +509,17 @@ class TPComm:
         outs = (C.c_void_p * world)(*[d.data_ptr() for d in dsts])
         check(comms[0].lib.s12_allreduce_f32_emulated_async(arr, world, ins, outs, srcs[0].numel(), _stream(stream)),
               "s12_allreduce_f32_emulated_async")
+
+    def set_wait_limit_ms(self, ms: int) -> int:
+        """How long a kernel waits for a peer before it gives up (default 2000 ms); returns the old limit."""
+        old = self.lib.s12_comm_set_wait_limit_ms(self._h, int(ms))
+        if old < 0:
+            check(old, "s12_comm_set_wait_limit_ms")
+        return old
+
+    def reset(self) -> None:
+        """After a call that gave up: zero this rank's receive areas and call counter (every rank calls it)."""
+        check(self.lib.s12_comm_reset(self._h), "s12_comm_reset")
 
     def close(self) -> None:
         if self._h:
