@@ -229,10 +229,10 @@ def test_flash_attention_names_forward_to_the_same_kernels(eng, S):
     pos = rng.integers(7000, long_seq, batch).astype(np.int32)
     pos[0] = long_seq - 1
     outb = torch.zeros((batch, n_head * hd), dtype=torch.int16, device="cuda")
-    rc = eng.lib.launch_flash_attention_batch(_cuda(qb).data_ptr(), _cuda(kcb).data_ptr(), _cuda(vcb).data_ptr(),
-                                              _cuda(skb).data_ptr(), _cuda(svb).data_ptr(), outb.data_ptr(),
-                                              _cuda(pos).data_ptr(), n_head, n_head_kv, hd, long_seq, scale, batch,
-                                              kv_stride, st)
+    dv = [_cuda(a) for a in (qb, kcb, vcb, skb, svb, pos)]          # kept alive until the kernel has run
+    rc = eng.lib.launch_flash_attention_batch(dv[0].data_ptr(), dv[1].data_ptr(), dv[2].data_ptr(), dv[3].data_ptr(),
+                                              dv[4].data_ptr(), outb.data_ptr(), dv[5].data_ptr(), n_head, n_head_kv, hd,
+                                              long_seq, scale, batch, kv_stride, st)
     assert rc == 0, eng.lib.s12_last_error()
     torch.cuda.synchronize()
     for s in (0, 7, batch - 1):
