@@ -286,6 +286,13 @@ def num_threads() -> int:
     return int(lib().s12o_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """Team size of the oracle's parallel loops, whatever OMP_NUM_THREADS says; returns the size in effect."""
+    L = lib()
+    L.s12o_set_num_threads.restype = C.c_int
+    return int(L.s12o_set_num_threads(C.c_int(int(n))))
+
+
 # ----------------------------------------------------------------------------
 # seeded synthetic tensors (stand-ins for real checkpoints)
 # ----------------------------------------------------------------------------

@@ -65,6 +65,20 @@ int s12o_num_threads(void)
 #endif
 }
 
+/* Sets the team size of the parallel loops below (a launcher such as torchrun
+ * exports OMP_NUM_THREADS=1 to every rank; the timed CPU baseline asks for the
+ * host's cores explicitly).  Returns the size now in effect. */
+int s12o_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 uint16_t s12o_decode_elem(uint8_t sm, uint8_t group, int base_exp)
 {
     return decode_elem(sm, group, base_exp);
