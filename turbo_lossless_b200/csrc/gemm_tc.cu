@@ -100,8 +100,9 @@ struct GemmParams {
     int split;                  // 0: stream-K ranges, >= 1: tiles cut into this many fixed parts
     int cluster;                // > 1: the `split` parts of a tile run as one thread-block cluster and add
                                 // their accumulators through distributed shared memory (no workspace)
-    int neg_base;               // some base_exp < 0: decode mode 1
+    int neg_base;               // some base_exp < 0: decode mode 1; 2: mode 0 with plain shifts (tuning knob)
     uint32_t tmem_cols;
+    DecodeMul mul;              // {128, 8, 1 << 24}: see decode8_fma
 };
 
 struct GemmMaps { CUtensorMap sm[kMaxGemmTensors]; CUtensorMap gr[kMaxGemmTensors]; };
@@ -295,8 +296,10 @@ __device__ __forceinline__ void esc_apply(EscCursor& e, const GemmTensor& T, int
 // order (= 32 TMEM columns of the thread's lane); escapes get the exponent
 // base_exp.  The raw boxes carry the 128-byte swizzle: 16-byte chunk j of row r
 // sits at chunk j ^ (r & 7).  Reading chunk by chunk keeps few raw registers live.
+// kMode 0: decode8_fma (shifts issued as multiplies on the FMA pipe: the ALU pipe is this kernel's busiest),
+// kMode 1: base_exp < 0, kMode 3: decode8<0> with plain shifts.
 template <int kMode>
-__device__ __forceinline__ void decode_row(const uint8_t* raw, int r, int sub, uint32_t base2, uint32_t (&v)[32])
+__device__ __forceinline__ void decode_row(const uint8_t* raw, int r, int sub, uint32_t base2, const DecodeMul& mul, uint32_t (&v)[32])
 {
     const uint8_t* srow = raw + (sub >> 1) * kRawBoxBytes + r * 128;
     const uint8_t* grow = raw + 2 * kRawBoxBytes + r * 128;
@@ -312,10 +315,12 @@ __device__ __forceinline__ void decode_row(const uint8_t* raw, int r, int sub, u
             const uint4 s = *reinterpret_cast<const uint4*>(srow + (((sc + c) ^ sw) << 4));
             const uint32_t gx = h ? gq.z : gq.x, gy = h ? gq.w : gq.y;
             uint32_t p[4];
-            decode8<kMode>(s.x, s.y, gx, base2, p);
+            if (kMode == 0) decode8_fma(s.x, s.y, gx, base2, mul, p);
+            else decode8<kMode == 3 ? 0 : kMode>(s.x, s.y, gx, base2, p);
             v[8 * c + 0] = prmt(p[0], p[1], 0x5410u); v[8 * c + 1] = prmt(p[2], p[3], 0x5410u);
             v[8 * c + 2] = prmt(p[0], p[1], 0x7632u); v[8 * c + 3] = prmt(p[2], p[3], 0x7632u);
-            decode8<kMode>(s.z, s.w, gy, base2, p);
+            if (kMode == 0) decode8_fma(s.z, s.w, gy, base2, mul, p);
+            else decode8<kMode == 3 ? 0 : kMode>(s.z, s.w, gy, base2, p);
             v[8 * c + 4] = prmt(p[0], p[1], 0x5410u); v[8 * c + 5] = prmt(p[2], p[3], 0x5410u);
             v[8 * c + 6] = prmt(p[0], p[1], 0x7632u); v[8 * c + 7] = prmt(p[2], p[3], 0x7632u);
         }
@@ -651,8 +656,9 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
             mbar_wait(b_rawfull + 8 * sr, wr & 1, P.status, 0x200u, &s_abort);
             const GemmTensor& T = P.t[tr.ti];
             uint32_t v[32];
-            if (P.neg_base) decode_row<1>(raw + sr * kRawBytes, t, gi, T.base2, v);
-            else decode_row<0>(raw + sr * kRawBytes, t, gi, T.base2, v);
+            if (P.neg_base == 0) decode_row<0>(raw + sr * kRawBytes, t, gi, T.base2, P.mul, v);
+            else if (P.neg_base == 1) decode_row<1>(raw + sr * kRawBytes, t, gi, T.base2, P.mul, v);
+            else decode_row<3>(raw + sr * kRawBytes, t, gi, T.base2, P.mul, v);
             __syncwarp();
             if (lane == 0) mbar_arrive(b_rawempty + 8 * sr);      // this warp has read its share of the stage
             esc_apply(esc, T, kb * kBigK + gi * kTK, v);
@@ -849,6 +855,8 @@ static int gemm_fill(GemmParams& P, GemmMaps& maps, CUtensorMap& mx, const S12Te
                   kTK, (uint32_t)P.BN, CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(S12_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed", who);
     P.tmem_cols = 512u;                  // accumulators below kATmemBase, the A stages above
+    P.mul.m128 = 128u; P.mul.m8 = 8u; P.mul.hi24 = 1u << 24;
+    if (!P.neg_base && env_knob("S12_GEMM_FMA", 1) == 0) P.neg_base = 2;
     return S12_OK;
 }
 
