@@ -151,6 +151,15 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr)
     asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
     return v;
 }
+// True in exactly one lane of a converged warp.  The single-thread tcgen05 instructions are issued under this
+// predicate rather than under `lane == 0`: measured on this part, four tcgen05.mma (N = 64) behind `if (lane == 0)`
+// issue at 80-160 cycles each, behind elect.sync at 37.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t leader;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(leader));
+    return leader != 0;
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
 {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
@@ -598,7 +607,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ----------------------------
         // The whole warp walks the schedule (uniform control flow, so that addresses and descriptors stay
-        // warp-uniform); lane 0 issues the MMAs and the commits.
+        // warp-uniform); one elected lane issues the MMAs and the commits.
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTM >> 4) << 24);
         const uint64_t bdesc0 = smem_desc_sw128(smem_addr(Xbuf));
         const uint64_t bstep = (uint64_t)(xbytes >> 4);
@@ -620,7 +629,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
                     tc_fence_after();
                     // look at the next stage now: the test's latency hides behind the MMA issue
                     ready = sub + 1 < kSub ? mbar_test(b_full + 8 * (sub + 1), wa & 1) : mbar_test(b_full, (wa + 1) & 1);
-                    if (lane == 0) {
+                    __syncwarp();
+                    if (elect_one()) {
                         const uint64_t bd = bdesc0 + (uint64_t)sub * bstep;
                         const uint32_t a_tmem = tmem_base + kATmemBase + (uint32_t)sub * kATmemCols;
 #pragma unroll
@@ -632,7 +642,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ CU
                     accumulate = 1;
                 }
             }
-            if (lane == 0) umma_commit(b_accfull + 8 * buf);     // accumulator of this tile segment is complete
+            __syncwarp();
+            if (elect_one()) umma_commit(b_accfull + 8 * buf);   // accumulator of this tile segment is complete
             __syncwarp();
             nacc++;
             tile_end += KB;
