@@ -292,6 +292,8 @@ class HotPath:
         self.logits = torch.empty(B, model["lm_head"].M, device=dev) if model["lm_head"] is not None else self.o_q
         self.tokens = torch.zeros(B, dtype=torch.int32, device=dev)
         self.launches = 0
+        self.sharded_argmax = False
+        self.vocab_lo = shard(cfg["vocab"], rank, world, 16)[0] if cfg["vocab"] else 0
         self.use_fused = comm is not None and comm_mode == "fused" and B == 1
         self.moe_blocks, self.router_logits = [], None
         if cfg.get("experts"):
@@ -365,6 +367,13 @@ class HotPath:
                         self._all_reduce(self.o_d)
         if m["lm_head"] is not None:
             self._add_k(lambda: self._proj([m["lm_head"]], self.x_hidden, [self.logits]))
+            if world > 1 and self.comm is not None:
+                # the output projection is split by rows: local argmax + the ranks' best pairs through the all-reduce
+                def tp_argmax():
+                    self.comm.tp_argmax(self.logits, self.vocab_lo, self.tokens)
+                    self.launches += 3
+                self._add_k(tp_argmax)
+                self.sharded_argmax = True
 
     def step(self):
         for kind, item in self.segments:
@@ -449,7 +458,7 @@ def measure_hot_path(torch, dist, hp, stream, steps, warmup, world, e2e_argmax):
     def e2e_step():
         hp.x_hidden.copy_(x_host, non_blocking=True)
         run()
-        if e2e_argmax:
+        if e2e_argmax and not hp.sharded_argmax:
             hp.argmax()
         res_host.copy_(res_dev, non_blocking=True)
         stream.synchronize()
@@ -500,11 +509,32 @@ def tp_check(torch, dist, eng, comm, model, hp, rank, world):
         gathered = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
         identical = identical and all(torch.equal(g, gathered[0]) for g in gathered)
-    t = torch.tensor([worst, 0.0 if identical else 1.0], device="cuda", dtype=torch.float64)
+    argmax_ok = None
+    if comm is not None and model["lm_head"] is not None:
+        if hp.B == 1:
+            eng.gemv([model["lm_head"]], hp.x_hidden, [hp.logits])
+        else:
+            eng.gemm_multi([model["lm_head"]], hp.x_hidden, [hp.logits], hp.x_hidden.shape[1], hp.B)
+        comm.tp_argmax(hp.logits, hp.vocab_lo, hp.tokens)
+        torch.cuda.synchronize()
+        sizes = torch.tensor([hp.logits.shape[1]], device="cuda")
+        all_sizes = [torch.zeros_like(sizes) for _ in range(world)]
+        dist.all_gather(all_sizes, sizes)
+        widest = int(max(int(x[0]) for x in all_sizes))
+        padded = torch.full((hp.B, widest), float("-inf"), device="cuda")
+        padded[:, :hp.logits.shape[1]] = hp.logits
+        gathered = [torch.empty_like(padded) for _ in range(world)]
+        dist.all_gather(gathered, padded)
+        whole = torch.cat([g[:, :int(n[0])] for g, n in zip(gathered, all_sizes)], dim=1)
+        argmax_ok = bool(torch.equal(whole.argmax(dim=1).to(torch.int32), hp.tokens))
+    t = torch.tensor([worst, 0.0 if identical else 1.0, 0.0 if argmax_ok in (None, True) else 1.0], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return {"max_rel_err": float(t[0]), "bit_identical_across_ranks": float(t[1]) == 0.0, "tolerance": 1e-5,
-            "ok": float(t[0]) <= 1e-5 and float(t[1]) == 0.0,
-            "what": "layer 0 o and down projections: own all-reduce vs torch.distributed all_reduce of the same partials"}
+    out = {"max_rel_err": float(t[0]), "bit_identical_across_ranks": float(t[1]) == 0.0, "tolerance": 1e-5,
+           "ok": float(t[0]) <= 1e-5 and float(t[1]) == 0.0 and float(t[2]) == 0.0,
+           "what": "layer 0 o and down projections: own all-reduce vs torch.distributed all_reduce of the same partials"}
+    if argmax_ok is not None:
+        out["sharded_argmax_equals_argmax_of_gathered_logits"] = float(t[2]) == 0.0
+    return out
 
 
 def run_ours(args):
@@ -544,7 +574,7 @@ def run_ours(args):
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        times, e2e = measure_hot_path(torch, dist, hp, stream, args.steps, args.warmup, world, e2e_argmax=B > 16)
+        times, e2e = measure_hot_path(torch, dist, hp, stream, args.steps, args.warmup, world, e2e_argmax=B > 16 or hp.sharded_argmax)
         clocks = sampler.stop() if rank == 0 else None
         ms = median(times)
         _log(f"timed region done: {ms / args.steps:.3f} ms/step over {len(times)} blocks")
@@ -811,7 +841,7 @@ def tp_70b_block(torch, dist, eng, comm, args, stream, rank, world, CompressedWe
     hp = HotPath(torch, dist, eng, model, cfg, 1, rank, world, comm, args.comm)
     check = tp_check(torch, dist, eng, comm, model, hp, rank, world)
     steps = max(4, args.steps // 2)
-    times, e2e = measure_hot_path(torch, dist, hp, stream, steps, 3, world, e2e_argmax=False)
+    times, e2e = measure_hot_path(torch, dist, hp, stream, steps, 3, world, e2e_argmax=hp.sharded_argmax)
     ms_step = median(times) / steps
     tens = model_tensors(model)
     tot = torch.tensor([float(sum(t.compressed_bytes for t in tens))], device="cuda", dtype=torch.float64)

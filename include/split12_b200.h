@@ -477,6 +477,18 @@ int s12_comm_set_wait_limit_ms(S12Comm* comm, int ms);
  * before and after, then the communicator is usable again. */
 int s12_comm_reset(S12Comm* comm);
 int s12_comm_destroy(S12Comm* comm);
+/* Greedy tokens when the output projection (lm_head) is split by rows across
+ * the ranks: `logits` holds this rank's n_local vocabulary rows of every
+ * sequence, fp32 [batch][n_local], covering the global indices
+ * [index_offset, index_offset + n_local).  result[batch] (int32, the same on
+ * every rank) equals launch_argmax_batch over the whole vocabulary, ties
+ * included.  batch <= 1024, vocabulary below 2^24.  The two kernels around the
+ * all-reduce are exported on their own: pairs is fp32 [world][batch][2]. */
+int s12_tp_argmax_async(S12Comm* comm, const float* logits, int n_local, int index_offset, int batch,
+                        int* result, void* stream);
+int s12_tp_argmax_partial_async(const float* logits, int n_local, int index_offset, int batch, int rank,
+                                int world, float* pairs, void* stream);
+int s12_tp_argmax_merge_async(const float* pairs, int world, int batch, int* result, void* stream);
 /* Test support for a single GPU: `world` communicators created in one process
  * on one device are wired to each other, and one cooperative launch runs all
  * ranks of a call side by side (ranks that wait on one another must never be

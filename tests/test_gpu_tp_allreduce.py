@@ -142,6 +142,53 @@ def test_wait_for_a_peer_that_never_arrives_runs_out(n):
         c.close()
 
 
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("batch,vocab", [(1, 32000), (5, 1000), (64, 128256)])
+def test_sharded_argmax_equals_argmax_over_the_whole_vocabulary(world, batch, vocab):
+    """Output projection split by rows: local argmax with global indices, pairs collected by the all-reduce (all
+    ranks emulated in one launch), merge.  Equal maxima in different shards are planted: the winner must be the one
+    launch_argmax_batch picks over the unsplit logits."""
+    import ctypes as C
+    import torch
+    from turbo_lossless_b200 import TPComm, Split12Engine
+    eng = Split12Engine()
+    lib = eng.lib
+    rng = np.random.default_rng(world * 7 + batch)
+    logits = rng.standard_normal((batch, vocab)).astype(np.float32)
+    for b in range(batch):                                   # ties across (and inside) shards
+        top = logits[b].max() + 1.0
+        for i in rng.integers(0, vocab, 3):
+            logits[b, i] = top
+    full = torch.from_numpy(logits).cuda()
+    want = torch.zeros(batch, dtype=torch.int32, device="cuda")
+    eng.argmax(full, want)
+    bounds = [(vocab // 16 * r // world) * 16 for r in range(world)] + [vocab]
+    comms = TPComm.local(world, 4096 * 8)
+    n = (2 * batch * world + 3) & ~3
+    pairs = [torch.full((max(n, 2 * batch * world),), float("nan"), device="cuda") for _ in range(world)]
+    st = torch.cuda.current_stream().cuda_stream
+    shards = [full[:, bounds[r]:bounds[r + 1]].contiguous() for r in range(world)]
+    for r in range(world):
+        assert lib.s12_tp_argmax_partial_async(shards[r].data_ptr(), bounds[r + 1] - bounds[r], bounds[r], batch, r, world,
+                                               pairs[r].data_ptr(), st) == 0
+        if n > 2 * batch * world:
+            pairs[r][2 * batch * world:] = 0
+    TPComm.all_reduce_emulated(comms, [p[:n] for p in pairs], [p[:n] for p in pairs])
+    for r in range(world):
+        got = torch.full((batch,), -1, dtype=torch.int32, device="cuda")
+        assert lib.s12_tp_argmax_merge_async(pairs[r].data_ptr(), world, batch, got.data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"rank {r}"
+    if world == 1:                                           # the composed call on a world of one
+        got = torch.full((batch,), -1, dtype=torch.int32, device="cuda")
+        comms[0].tp_argmax(full, 0, got)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    assert eng.device_status() == 0
+    for c in comms:
+        c.close()
+
+
 _WORKER = r"""
 import os, sys
 import numpy as np, torch, torch.distributed as dist
@@ -181,6 +228,18 @@ for call, (M, K) in enumerate([(4096, 4096), (4096, 14336), (1000, 1024), (1000,
     gathered = [None] * world
     dist.all_gather_object(gathered, got.tobytes())
     ok = ok and all(g == gathered[0] for g in gathered)      # bit-identical on every rank
+# output projection split by rows: the sharded argmax equals the argmax over the gathered logits
+V, Bq = 32000, 4
+logits = np.random.default_rng(9).standard_normal((Bq, V)).astype(np.float32)
+logits[:, 100] = logits[:, V - 7] = 50.0                     # a tie between the first and the last shard
+lo, hi = V // world * rank, V // world * (rank + 1)
+mine = torch.from_numpy(np.ascontiguousarray(logits[:, lo:hi])).cuda()
+tok = torch.full((Bq,), -1, dtype=torch.int32, device="cuda")
+comm.tp_argmax(mine, lo, tok)
+want = torch.zeros(Bq, dtype=torch.int32, device="cuda")
+eng.argmax(torch.from_numpy(logits).cuda(), want)
+torch.cuda.synchronize()
+ok = ok and torch.equal(tok, want) and eng.device_status() == 0
 dist.barrier()
 comm.close()
 dist.destroy_process_group()

@@ -92,6 +92,9 @@ SIGNATURES = {
     "s12_comm_set_wait_limit_ms": (_i, [_vp, _i]),
     "s12_comm_reset": (_i, [_vp]),
     "s12_comm_destroy": (_i, [_vp]),
+    "s12_tp_argmax_async": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
+    "s12_tp_argmax_partial_async": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp]),
+    "s12_tp_argmax_merge_async": (_i, [_vp, _i, _i, _vp, _vp]),
 }
 
 _lib = None

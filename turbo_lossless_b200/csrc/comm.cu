@@ -123,6 +123,8 @@ allreduce_ll_kernel(const __grid_constant__ AllReduceParams P)
 // ----------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------
+constexpr int kTpArgmaxMaxBatch = 1024;
+
 struct S12Comm {
     int rank = 0, world = 1, device = 0;
     int capacity = 0;                         // floats per receive row
@@ -132,6 +134,7 @@ struct S12Comm {
     bool opened[s12::kCommMaxWorld] = {};      // mapped through an IPC handle (must be closed)
     unsigned int* calls = nullptr;             // [0] calls completed, [1] CTAs done in the running call
     unsigned long long wait_ns = s12::kPeerWaitLimitNs;   // bound of a wait for a peer
+    float* pairs = nullptr;                    // scratch of s12_tp_argmax_async: [world][kTpArgmaxMaxBatch][2]
     bool connected = false;
 };
 
@@ -160,13 +163,14 @@ int s12_comm_create(int rank, int world, long long max_floats, S12Comm** out, vo
     if (!rc) rc = check_cuda(cudaMemset(c->base, 0, total), who);
     if (!rc) rc = check_cuda(cudaMalloc(&c->calls, 2 * sizeof(unsigned int)), who);
     if (!rc) rc = check_cuda(cudaMemset(c->calls, 0, 2 * sizeof(unsigned int)), who);
+    if (!rc) rc = check_cuda(cudaMalloc(&c->pairs, (size_t)2 * world * kTpArgmaxMaxBatch * sizeof(float)), who);
     if (!rc && handle_out) {
         cudaIpcMemHandle_t h;
         rc = check_cuda(cudaIpcGetMemHandle(&h, c->base), who);
         if (!rc) memcpy(handle_out, &h, sizeof h);
     }
     if (!rc) rc = check_cuda(cudaDeviceSynchronize(), who);
-    if (rc) { if (c->base) cudaFree(c->base); if (c->calls) cudaFree(c->calls); delete c; return rc; }
+    if (rc) { if (c->base) cudaFree(c->base); if (c->calls) cudaFree(c->calls); if (c->pairs) cudaFree(c->pairs); delete c; return rc; }
     c->peer_base[rank] = c->base;
     *out = c;
     return S12_OK;
@@ -311,8 +315,27 @@ int s12_comm_destroy(S12Comm* c)
         if (c->opened[p] && c->peer_base[p]) cudaIpcCloseMemHandle(c->peer_base[p]);
     if (c->base) cudaFree(c->base);
     if (c->calls) cudaFree(c->calls);
+    if (c->pairs) cudaFree(c->pairs);
     delete c;
     return S12_OK;
+}
+
+// Greedy tokens of `batch` sequences when the output projection is split by rows: local argmax with global indices,
+// the ranks' {value, index} pairs collected by one small all-reduce (every slot has one non-zero contributor, so the
+// sums are exact), then the best pair per sequence.  Three launches, capturable.
+int s12_tp_argmax_async(S12Comm* c, const float* logits, int n_local, int index_offset, int batch, int* result, void* stream)
+{
+    using namespace s12;
+    const char* who = "s12_tp_argmax_async";
+    if (!c || !logits || !result) return fail(S12_ERR_BAD_ARG, "%s: null argument", who);
+    if (!c->connected) return fail(S12_ERR_BAD_ARG, "%s: communicator not connected", who);
+    if (batch < 1 || batch > kTpArgmaxMaxBatch) return fail(S12_ERR_TOO_LARGE, "%s: batch=%d outside 1..%d", who, batch, kTpArgmaxMaxBatch);
+    const int n = (2 * batch * c->world + 3) & ~3;
+    if (n > c->capacity) return fail(S12_ERR_TOO_LARGE, "%s: the communicator's capacity %d is below %d floats", who, c->capacity, n);
+    int rc = s12_tp_argmax_partial_async(logits, n_local, index_offset, batch, c->rank, c->world, c->pairs, stream);
+    if (!rc) rc = s12_allreduce_f32_async(c, c->pairs, c->pairs, n, stream);
+    if (!rc) rc = s12_tp_argmax_merge_async(c->pairs, c->world, batch, result, stream);
+    return rc;
 }
 
 }  // extern "C"

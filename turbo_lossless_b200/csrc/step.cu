@@ -479,8 +479,13 @@ __device__ __forceinline__ bool argmax_better(float v, int i, float bv, int bi)
     const unsigned r = __brev((unsigned)i & 255u), br = __brev((unsigned)bi & 255u);
     return r < br || (r == br && i < bi);
 }
+// With `pairs` given (tensor-parallel output projection: this rank holds `n` of the vocabulary's rows, starting at
+// index_offset) the winner is not stored as a token but as the pair {value, global index as float} in this rank's
+// slot of pairs[slot][sequence][2], and the other ranks' slots are zeroed, so that a sum over ranks collects every
+// rank's pair.  Ties are decided on the GLOBAL index, so the merged result equals the argmax over the whole vocabulary.
 __global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, int* __restrict__ result, int n)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ result, int n, int index_offset, float* __restrict__ pairs,
+              int pair_slot, int pair_slots)
 {
     __shared__ float sv[32];
     __shared__ int si[32];
@@ -488,7 +493,7 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ result, int n)
     grid_dependency_wait();
     const float* row = logits + (size_t)blockIdx.x * n;
     float bv = -INFINITY;
-    int bi = 0;
+    int bi = index_offset;
     if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {   // 16-byte aligned rows: four elements per load, two in flight
         const float4* r4 = reinterpret_cast<const float4*>(row);
         for (int i = threadIdx.x; i < n / 4; i += 2 * blockDim.x) {
@@ -497,16 +502,16 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ result, int n)
             const float4 b = j < n / 4 ? r4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
             const float va[4] = {a.x, a.y, a.z, a.w}, vb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-            for (int e = 0; e < 4; e++) if (argmax_better(va[e], 4 * i + e, bv, bi)) { bv = va[e]; bi = 4 * i + e; }
+            for (int e = 0; e < 4; e++) if (argmax_better(va[e], index_offset + 4 * i + e, bv, bi)) { bv = va[e]; bi = index_offset + 4 * i + e; }
             if (j < n / 4) {
 #pragma unroll
-                for (int e = 0; e < 4; e++) if (argmax_better(vb[e], 4 * j + e, bv, bi)) { bv = vb[e]; bi = 4 * j + e; }
+                for (int e = 0; e < 4; e++) if (argmax_better(vb[e], index_offset + 4 * j + e, bv, bi)) { bv = vb[e]; bi = index_offset + 4 * j + e; }
             }
         }
     } else {
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             const float v = row[i];
-            if (argmax_better(v, i, bv, bi)) { bv = v; bi = i; }
+            if (argmax_better(v, index_offset + i, bv, bi)) { bv = v; bi = index_offset + i; }
         }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -528,8 +533,33 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ result, int n)
             const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
             if (argmax_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
         }
-        if (lane == 0) result[blockIdx.x] = bi == 0x7FFFFFFF ? 0 : bi;
+        if (bi == 0x7FFFFFFF) bi = index_offset;
+        if (pairs == nullptr) {
+            if (lane == 0) result[blockIdx.x] = bi;
+        } else if (lane < pair_slots) {
+            float2 pr = make_float2(0.f, 0.f);
+            if (lane == pair_slot) pr = make_float2(bv, (float)bi);
+            reinterpret_cast<float2*>(pairs)[(size_t)lane * gridDim.x + blockIdx.x] = pr;
+        }
     }
+}
+
+// Picks, per sequence, the best of the ranks' {value, index} pairs (same order as argmax_kernel).
+__global__ void __launch_bounds__(256)
+argmax_merge_kernel(const float* __restrict__ pairs, int world, int batch, int* __restrict__ result)
+{
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    float bv = -INFINITY;
+    int bi = 0x7FFFFFFF;
+    for (int r = 0; r < world; r++) {
+        const float2 pr = reinterpret_cast<const float2*>(pairs)[(size_t)r * batch + b];
+        const int i = (int)pr.y;
+        if (bi == 0x7FFFFFFF || argmax_better(pr.x, i, bv, bi)) { bv = pr.x; bi = i; }
+    }
+    result[b] = bi;
 }
 
 // frequencies as the engine computes them on the host (engine/kernels.hip:129-140)
@@ -622,7 +652,22 @@ int launch_embed_lookup(const int16_t* embd_table, const int* token_ids, float* 
 int launch_argmax_batch(const float* logits, int* results, int n_vocab, int batch_size, void* stream)
 {
     if (!logits || !results || n_vocab < 1 || batch_size < 1) return fail(S12_ERR_BAD_ARG, "launch_argmax: bad argument");
-    return launch(argmax_kernel, dim3(batch_size), dim3(1024), 0, stream, "launch_argmax", logits, results, n_vocab);
+    return launch(argmax_kernel, dim3(batch_size), dim3(1024), 0, stream, "launch_argmax", logits, results, n_vocab, 0, (float*)nullptr, 0, 0);
+}
+int s12_tp_argmax_partial_async(const float* logits, int n_local, int index_offset, int batch, int rank, int world, float* pairs,
+                                void* stream)
+{
+    if (!logits || !pairs || n_local < 1 || batch < 1 || world < 1 || world > 32 || rank < 0 || rank >= world || index_offset < 0 ||
+        (long long)index_offset + n_local > (1 << 24))
+        return fail(S12_ERR_BAD_ARG, "s12_tp_argmax_partial_async: bad argument (indices must stay below 2^24)");
+    return launch(argmax_kernel, dim3(batch), dim3(1024), 0, stream, "s12_tp_argmax_partial_async", logits, (int*)nullptr, n_local,
+                  index_offset, pairs, rank, world);
+}
+int s12_tp_argmax_merge_async(const float* pairs, int world, int batch, int* result, void* stream)
+{
+    if (!pairs || !result || world < 1 || batch < 1) return fail(S12_ERR_BAD_ARG, "s12_tp_argmax_merge_async: bad argument");
+    return launch(argmax_merge_kernel, dim3((batch + 255) / 256), dim3(256), 0, stream, "s12_tp_argmax_merge_async", pairs, world,
+                  batch, result);
 }
 int launch_argmax(const float* logits, int* result, int n, void* stream) { return launch_argmax_batch(logits, result, n, 1, stream); }
 

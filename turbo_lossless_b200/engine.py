@@ -510,6 +510,12 @@ class TPComm:
         check(comms[0].lib.s12_allreduce_f32_emulated_async(arr, world, ins, outs, srcs[0].numel(), _stream(stream)),
               "s12_allreduce_f32_emulated_async")
 
+    def tp_argmax(self, logits: torch.Tensor, index_offset: int, result: torch.Tensor, stream=None) -> None:
+        """Greedy tokens from this rank's rows of the output projection: fp32 [batch][n_local] -> int32 [batch]."""
+        batch, n_local = (1, logits.numel()) if logits.dim() == 1 else logits.shape
+        check(self.lib.s12_tp_argmax_async(self._h, _ptr(logits), n_local, index_offset, batch, _ptr(result), _stream(stream)),
+              "s12_tp_argmax_async")
+
     def set_wait_limit_ms(self, ms: int) -> int:
         """How long a kernel waits for a peer before it gives up (default 2000 ms); returns the old limit."""
         old = self.lib.s12_comm_set_wait_limit_ms(self._h, int(ms))
