@@ -221,7 +221,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             // units 2*t4, 2*t4+1 (low run) and 8+2*t4, 8+2*t4+1 (high run) as its
             // loads j = 0..3, each from position j*4 + t4
             const int c = u >> 7, uu = u & 127, w16 = uu & 15;
-            const int pos = (((w16 >> 3) << 1) + (w16 & 1)) * 4 + ((w16 & 7) >> 1);
+            const int hi = (w16 >> 3) ^ ((kSwap && Q >= 2) ? (c & 1) : 0);      // odd chunks: runs the other way round
+            const int pos = ((hi << 1) + (w16 & 1)) * 4 + ((w16 & 7) >> 1);
             xperm[xchunk_base(c) + (uu & ~15) + pos] = pv;
         }
         named_bar_sync(1, kConsumers * 32);
@@ -230,21 +231,37 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
         // wi takes columns [wi*128, wi*128+128) of every segment
         const int grp = warp / kGroupWarps, wi = warp % kGroupWarps;
         const int g = lane >> 2, t4 = lane & 3;
+        // Which tile segment an MMA row stands for.  Plain map: row m = chunk m / R, tile row m % R.  All segments
+        // start on the same shared-memory bank (they are 1024 bytes apart), so in every 8-lane phase of a 16-byte
+        // load the lanes of rows g and g + 1 collide.  Parity map (kSwap, two or more chunks per tile): the rows
+        // of even g stand for even chunks, those of odd g for odd chunks,
+        //     chunk = (m & 1) + 2 * ((m >> 1) / R),   tile row = (m >> 1) % R,
+        // and everything that belongs to an odd chunk is read the other way round: the thread's two 16-column
+        // runs in the opposite order, from the neighbouring 128-column window (w ^ 1), with the activations of odd
+        // chunks staged to match.  The MMA only needs A row m and B column chunk(m) to agree on the order of k,
+        // and a thread's rows g and g + 8 and its B column g all have the parity of g; so the loop is the same
+        // instruction for instruction, every lane just starts from other offsets -- sm loads are then free of
+        // conflicts, gr loads two-way.
+        const bool parity_map = kSwap && Q >= 2;
+        const int b = parity_map ? (g & 1) : 0;
         const int qx = g % Q;                                // chunk whose activations this thread feeds
-        const int qA = g / R, qB = (g + 8) / R;              // chunk (= result column) of segments g, g+8
-        const int rA = g % R, rB = (g + 8) % R;              // tile row of segments g, g+8
-        // Inside its warp's 128-column window a thread owns two runs of 16
-        // columns: [t4*16, +16) and [64 + t4*16, +16).  All segments start on the
-        // same bank, so lanes with odd g fetch the two runs in the opposite
-        // order (and swap them back in registers): in every 8-lane phase of a
-        // 16-byte load the even-g lanes then hit the low 64 bytes of the window
-        // and the odd-g lanes the high 64 bytes.
-        const uint32_t odd = kSwap ? (g & 1) : 0u;   // kSwap off: plain order, two-way conflicts, no selects
-        const uint32_t offA = (rA * Q + qA) * kSegCols + wi * 128 + t4 * 16;
-        const uint32_t offB = (rB * Q + qB) * kSegCols + wi * 128 + t4 * 16;
-        const uint32_t goffA = kGrBase + (rA * Q + qA) * (kSegCols / 2) + wi * 64 + t4 * 8;
-        const uint32_t goffB = kGrBase + (rB * Q + qB) * (kSegCols / 2) + wi * 64 + t4 * 8;
-        const uint32_t first = odd * 64, second = 64 - first;
+        int qA, qB, rA, rB;                                  // chunk (= result column) and tile row of MMA rows g, g + 8
+        if (parity_map) {
+            const int iA = g >> 1, iB = (g + 8) >> 1;
+            qA = b + 2 * (iA / R); rA = iA % R;
+            qB = b + 2 * (iB / R); rB = iB % R;
+        } else {
+            qA = g / R; qB = (g + 8) / R;
+            rA = g % R; rB = (g + 8) % R;
+        }
+        const int segA = qA * R + rA, segB = qB * R + rB;    // where the epilogue expects the two sums
+        const int win = wi ^ b;                              // 128-column window of every segment this thread reads
+        // Inside the window a thread owns two runs of 16 columns: [t4*16, +16) and [64 + t4*16, +16).
+        const uint32_t offA = (rA * Q + qA) * kSegCols + win * 128 + t4 * 16;
+        const uint32_t offB = (rB * Q + qB) * kSegCols + win * 128 + t4 * 16;
+        const uint32_t goffA = kGrBase + (rA * Q + qA) * (kSegCols / 2) + win * 64 + t4 * 8;
+        const uint32_t goffB = kGrBase + (rB * Q + qB) * (kSegCols / 2) + win * 64 + t4 * 8;
+        const uint32_t first = b * 64, second = 64 - first;
 
         float acc[2][4];
 #pragma unroll
@@ -270,17 +287,16 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
             const uint4 bs = *reinterpret_cast<const uint4*>(st + offB + second);
             const uint2 gbf = *reinterpret_cast<const uint2*>(st + goffB + (first >> 1));
             const uint2 gbs = *reinterpret_cast<const uint2*>(st + goffB + (second >> 1));
-            const uint4* xp = xperm + (xchunk_base(kt * Q + qx) + wi * 16 + t4);
+            const uint4* xp = xperm + (xchunk_base(kt * Q + qx) + win * 16 + t4);
             uint4 xq[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) xq[j] = xp[j * 4];
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);   // stage data is in registers
 
-            const uint4 a0 = odd ? as : af, a1 = odd ? af : as;      // low run, high run
-            const uint4 b0v = odd ? bs : bf, b1v = odd ? bf : bs;
-            const uint2 ga0 = odd ? gas : gaf, ga1 = odd ? gaf : gas;
-            const uint2 gb0 = odd ? gbs : gbf, gb1 = odd ? gbf : gbs;
+            // first / second run as loaded: for an odd chunk that is high / low, and its activations are staged likewise
+            const uint4 a0 = af, a1 = as, b0v = bf, b1v = bs;
+            const uint2 ga0 = gaf, ga1 = gas, gb0 = gbf, gb1 = gbs;
             const uint32_t sa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             const uint32_t sb[8] = {b0v.x, b0v.y, b0v.z, b0v.w, b1v.x, b1v.y, b1v.z, b1v.w};
             const uint32_t gaw[4] = {ga0.x, ga0.y, ga1.x, ga1.y};
@@ -309,8 +325,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams P)
                 float* r = red + (slot * kConsumers + warp) * 16;
                 const float c0 = acc[0][0] + acc[1][0], c1 = acc[0][1] + acc[1][1];
                 const float c2 = acc[0][2] + acc[1][2], c3 = acc[0][3] + acc[1][3];
-                if (t4 == (qA >> 1)) r[g] = (qA & 1) ? c1 : c0;
-                if (t4 == (qB >> 1)) r[g + 8] = (qB & 1) ? c3 : c2;
+                if (t4 == (qA >> 1)) r[segA] = (qA & 1) ? c1 : c0;
+                if (t4 == (qB >> 1)) r[segB] = (qB & 1) ? c3 : c2;
 #pragma unroll
                 for (int a = 0; a < 2; a++)
 #pragma unroll
@@ -485,7 +501,7 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     const size_t smem = fixed + (size_t)depth * kStageBytes;
 
     typedef void (*Kern)(const StreamParams);
-    const int swap = env_knob("S12_GEMV_SWAP", 0) ? 1 : 0;   // 0: plain load order (fewer instructions, measured faster)
+    const int swap = env_knob("S12_GEMV_SWAP", 1) ? 1 : 0;   // 1: parity map of MMA rows to segments (sm loads free of bank conflicts)
     static const Kern table[2][2][3] = {
         {{gemv_stream_kernel<0, 1, false>, gemv_stream_kernel<1, 1, false>, gemv_stream_kernel<2, 1, false>},
          {gemv_stream_kernel<0, 2, false>, gemv_stream_kernel<1, 2, false>, gemv_stream_kernel<2, 2, false>}},
