@@ -610,7 +610,7 @@ def run_ours(args):
     ms_step = ms / args.steps
     toks = B * 1e3 / ms_step
     per_gpu_gbs = (total_bytes / world) / (ms_step * 1e-3) / 1e9
-    kernel = "gemv_stream_kernel" if B == 1 else ("gemm_tc_kernel" if B > 128 else ("gemm_stream_kernel" if B > 16 else "gemv_kernel"))
+    kernel = "gemv_stream_kernel" if B == 1 else ("gemm_tc_kernel" if B > 16 else "gemv_kernel")
     if B >= 128:
         roof = roofline_tensor(2.0 * total_weights * B / world / (ms_step * 1e-3) / 1e12, tf_sus, tf_burst, peak_src, kernel,
                                total_bytes / world, TRAFFIC_RATIO.get(kernel))

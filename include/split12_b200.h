@@ -184,7 +184,7 @@ int s12_gemv_batched_async(const S12Tensor* w, const void* act, int act_stride,
                            void* out, int out_stride, int B, void* stream);
 
 /* Batched decode + GEMM, any B >= 1 (dispatches by B: the GEMV family for
- * B <= 16, the streaming kernel for 16 < B <= 128, the tensor cores above).
+ * B <= 16, the tensor-core kernel above; one kernel serves every B > 16).
  * Exact escapes when w carries its CSR list.
  * All s12_gemm_* / nv_launch_split12_*gemm* calls of one device share one
  * partial-tile workspace (allocated by s12_init or by the first such call):
