@@ -8,7 +8,7 @@ import sys
 _PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_PATH = os.path.join(_PKG, "libsplit12_b200.so")
-SOURCES = ["runtime.cu", "decompress.cu", "patches.cu", "gemv.cu", "gemv_stream.cu", "gemm.cu", "gemm_tc.cu", "pack.cu", "comm.cu", "step.cu", "loader.cu", "moe.cu", "host.cpp"]
+SOURCES = ["runtime.cu", "decompress.cu", "patches.cu", "gemv.cu", "gemv_stream.cu", "gemm.cu", "gemm_tc.cu", "gemm_stream.cu", "pack.cu", "comm.cu", "step.cu", "loader.cu", "moe.cu", "host.cpp"]
 # sources compiled without --use_fast_math: the decode-step kernels use sincosf / expf / division on values
 # where the fast intrinsics lose digits (RoPE angles of hundreds of radians)
 ACCURATE_MATH = {"step.cu", "moe.cu"}

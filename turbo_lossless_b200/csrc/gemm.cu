@@ -1,8 +1,10 @@
 // Batched decode + GEMM entry points and their dispatcher.
 //
-//   B <= 16 : the MMA GEMV family (gemv.cu), HBM-bound.
-//   B  > 16 : the tcgen05 / TMEM kernel (gemm_tc.cu) when the shape qualifies,
-//             else the GEMV family over 16-column slices of the batch.
+//   2 <= B <= 16 : the streaming mma.sync kernel (gemm_stream.cu) on tensors of 48 row tiles or more, HBM-bound
+//                  (up to B = 32 when a tuning knob asks for it);
+//   B <= 16      : else the MMA GEMV family (gemv.cu);
+//   B  > 16      : the tcgen05 / TMEM kernel (gemm_tc.cu) when the shape qualifies,
+//                  else the GEMV family over 16-column slices of the batch.
 #include "common.cuh"
 
 namespace s12 {
@@ -15,6 +17,9 @@ int gemm_tc_launch(const S12Tensor* w, const void* act, int act_stride, void* ou
 int gemm_tc_launch_multi(const S12Tensor* w, int nt, const void* act, int act_stride, void* const* outs,
                          const int* out_strides, int B, void* stream, const char* who, const int* act_row0);
 
+int gemm_stream_try(const S12Tensor* w, int nt, const void* act, int act_stride, void* const* outs,
+                    const int* out_strides, int B, void* stream, const char* who, int* rc_out);
+
 int gemm_dispatch(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
                   int B, void* stream, const char* who)
 {
@@ -25,6 +30,12 @@ int gemm_dispatch(const S12Tensor* w, const void* act, int act_stride, void* out
     if (!act || !out) return fail(S12_ERR_BAD_ARG, "%s: null activations/output", who);
     if (act_stride < w->K || out_stride < w->M)
         return fail(S12_ERR_BAD_ARG, "%s: act_stride=%d (K=%d) out_stride=%d (M=%d)", who, act_stride, w->K, out_stride, w->M);
+    if (B >= 2 && B <= 32) {                                      // the streaming kernel for small batches
+        int rc = S12_OK;
+        void* outs[1] = {out};
+        const int strides[1] = {out_stride};
+        if (gemm_stream_try(w, 1, act, act_stride, outs, strides, B, stream, who, &rc) != 0) return rc;
+    }
     if (B > 16 && gemm_tc_supported(w, act_stride, out_stride, B))
         return gemm_tc_launch(w, act, act_stride, out, out_stride, B, stream, who);
     for (int b0 = 0; b0 < B; b0 += 16) {

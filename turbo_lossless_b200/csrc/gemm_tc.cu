@@ -262,17 +262,24 @@ struct EscCursor {
     uint32_t v0, v1;            // their exact bf16 bit patterns
 };
 constexpr int kNoEscape = 0x7FFFFFFF;
+// Index of the first entry of `row` with column >= kstart, and the end of the row's list.  Out of line (it
+// runs once per tile); the cursor itself is filled by the inlined caller so that it stays in registers.
+__device__ __noinline__ int2 esc_find(const int* __restrict__ row_off, const int* __restrict__ cols, int row, int kstart)
+{
+    int a = row_off[row], b = row_off[row + 1];
+    const int end = b;
+    while (a < b) { const int mid = (a + b) >> 1; if (cols[mid] < kstart) a = mid + 1; else b = mid; }
+    return make_int2(a, end);
+}
 // Positions the cursor on the first entry of `row` with column >= kstart.
-__device__ __noinline__ void esc_seek(EscCursor& e, const GemmTensor& T, int row, int kstart)
+__device__ __forceinline__ void esc_seek(EscCursor& e, const GemmTensor& T, int row, int kstart)
 {
     e.pos = e.end = 0; e.c0 = e.c1 = kNoEscape; e.v0 = e.v1 = 0;
     if (T.row_off == nullptr || row >= T.M) return;
-    int a = T.row_off[row], b = T.row_off[row + 1];
-    e.end = b;
-    while (a < b) { const int mid = (a + b) >> 1; if (T.cols[mid] < kstart) a = mid + 1; else b = mid; }
-    e.pos = a;
-    if (a < e.end) { e.c0 = T.cols[a]; e.v0 = (uint16_t)T.correct[a]; }
-    if (a + 1 < e.end) { e.c1 = T.cols[a + 1]; e.v1 = (uint16_t)T.correct[a + 1]; }
+    const int2 pe = esc_find(T.row_off, T.cols, row, kstart);
+    e.pos = pe.x; e.end = pe.y;
+    if (e.pos < e.end) { e.c0 = T.cols[e.pos]; e.v0 = (uint16_t)T.correct[e.pos]; }
+    if (e.pos + 1 < e.end) { e.c1 = T.cols[e.pos + 1]; e.v1 = (uint16_t)T.correct[e.pos + 1]; }
 }
 __device__ __forceinline__ void esc_advance(EscCursor& e, const GemmTensor& T)
 {
@@ -816,6 +823,24 @@ static int get_scratch(Scratch& out, const char* who)
         s.ws_bytes = ws_bytes;
     }
     out = s;
+    return S12_OK;
+}
+
+// For the other TMA-fed kernels of the library (gemm_stream.cu): a 2-D tiled map with the 128-byte swizzle over
+// bytes or bf16, whether the driver entry point exists, and the per-device GEMM workspace with its flags.
+bool tma_encode_2d(CUtensorMap* m, int dtype_bf16, const void* base, uint64_t inner, uint64_t outer,
+                   uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer)
+{
+    return make_map(m, dtype_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, base, inner, outer,
+                    row_stride_bytes, box_inner, box_outer, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+bool tma_available() { return encode_fn() != nullptr; }
+int gemm_workspace(float** ws, unsigned int** flags, size_t* slot_floats, const char* who)
+{
+    Scratch sc;
+    const int rc = get_scratch(sc, who);
+    if (rc) return rc;
+    *ws = sc.ws; *flags = sc.flags; *slot_floats = (size_t)256 * kTileRows;
     return S12_OK;
 }
 

@@ -493,6 +493,9 @@ int gemv_dispatch(const GemvCall& c, void* stream)
     return rc;
 }
 
+int gemm_stream_try(const S12Tensor* w, int nt, const void* act, int act_stride, void* const* outs,
+                    const int* out_strides, int B, void* stream, const char* who, int* rc_out);   // gemm_stream.cu
+
 // Strided batched form used by s12_gemv_batched_async and the GEMM dispatcher.
 int gemv_strided(const S12Tensor* w, const void* act, int act_stride, void* out, int out_stride,
                  int B, void* stream, const char* who)
@@ -541,7 +544,15 @@ int s12_gemv_allreduce_async(S12Comm* comm, const S12Tensor* w, const void* act,
 int s12_gemv_batched_async(const S12Tensor* w, const void* act, int act_stride,
                            void* out, int out_stride, int B, void* stream)
 {
-    return s12::gemv_strided(w, act, act_stride, out, out_stride, B, stream, "s12_gemv_batched_async");
+    using namespace s12;
+    const char* who = "s12_gemv_batched_async";
+    if (w && act && out && B >= 2 && B <= 16 && w->M > 0 && w->K > 0 && act_stride >= w->K && out_stride >= w->M) {
+        int rc = S12_OK;                                          // the streaming kernel for small batches
+        void* outs[1] = {out};
+        const int strides[1] = {out_stride};
+        if (gemm_stream_try(w, 1, act, act_stride, outs, strides, B, stream, who, &rc) != 0) return rc;
+    }
+    return gemv_strided(w, act, act_stride, out, out_stride, B, stream, who);
 }
 
 static int legacy_gemv(const void* sm, const void* gr, int base_exp, const void* act, void* out,
