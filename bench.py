@@ -18,7 +18,7 @@ block).  SM clocks and throttle reasons are sampled over all blocks.
 
 With one GPU and the default workload the line carries further blocks measured
 in the same process, each with its own roofline: `b256` (Llama-3.1-8B shape at
-B=256), `full_step` (every kernel of the decode step), `config1` (rotating
+B=256), `b16` (the default model at B=16, the small-batch range), `full_step` (every kernel of the decode step), `config1` (rotating
 4096 x 4096 tensors, GEMV GB/s), `decompress` (stand-alone split12 -> bf16) and
 `ref_gpu` (the reference's own CUDA kernels, when oracle/_ref holds them, timed
 on the same tensors through the same entry-point names).
@@ -48,6 +48,8 @@ if ROOT not in sys.path:
 WORKLOADS = {
     "mistral7b_b1": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=32000, batch=1,
                          desc="Mistral-7B-shaped decode step at B=1 (BASELINE configs[1]): all split12 projections"),
+    "mistral7b_b16": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=32000, batch=16,
+                          desc="Mistral-7B-shaped decode step at B=16 (the engine's small-batch range): all split12 projections"),
     "llama8b_b1": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=128256, batch=1,
                        desc="Llama-3.1-8B-shaped decode step at B=1: all split12 projections"),
     "llama8b_b256": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=128256, batch=256,
@@ -76,7 +78,7 @@ WORKLOADS = {
 
 
 # (dram read + write) / packed bytes measured with ncu on one-layer runs (summaries under profiles/), per dominant kernel
-TRAFFIC_RATIO = {"gemv_stream_kernel": 1.022, "gemm_tc_kernel": 1.154}
+TRAFFIC_RATIO = {"gemv_stream_kernel": 1.022, "gemm_tc_kernel": 1.154, "gemm_stream_kernel": 1.020}
 MIN_TIMED_MS = 500.0          # blocks of K steps are repeated until this much device time is covered
 
 
@@ -91,7 +93,7 @@ def parse_args():
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--blocks", default="auto", choices=["auto", "none"],
-                    help="auto: the default workload also measures b256 / full_step / config1 / decompress / ref_gpu on one "
+                    help="auto: the default workload also measures b256 / b16 / full_step / config1 / decompress / ref_gpu on one "
                          "GPU and a Llama-3-70B-shaped block on several; none: the named workload only")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (development only)")
     ap.add_argument("--comm", default="own", choices=["own", "fused", "nccl"],
@@ -610,7 +612,7 @@ def run_ours(args):
     ms_step = ms / args.steps
     toks = B * 1e3 / ms_step
     per_gpu_gbs = (total_bytes / world) / (ms_step * 1e-3) / 1e9
-    kernel = "gemv_stream_kernel" if B == 1 else ("gemm_tc_kernel" if B > 16 else "gemv_kernel")
+    kernel = "gemv_stream_kernel" if B == 1 else ("gemm_tc_kernel" if B > 16 else "gemm_stream_kernel")
     if B >= 128:
         roof = roofline_tensor(2.0 * total_weights * B / world / (ms_step * 1e-3) / 1e12, tf_sus, tf_burst, peak_src, kernel,
                                total_bytes / world, TRAFFIC_RATIO.get(kernel))
@@ -678,6 +680,23 @@ def single_gpu_blocks(torch, eng, model, args, stream, CompressedWeight):
                    "e2e": e2e, "gpu_launches": hp.launches_per_step * steps * len(times), "clocks": clocks,
                    "timing_blocks_ms": {"n": len(times), "min": round(min(times), 3), "max": round(max(times), 3)}}
     del hp, m2, lm
+    torch.cuda.empty_cache()
+
+    # ---- b16: the same model at B = 16, the small-batch range (HBM-bound: streaming kernel on the tensors of 48 row
+    # tiles or more, the GEMV family on the 4096-row ones)
+    cfg = WORKLOADS["mistral7b_b16"]
+    hp = HotPath(torch, None, eng, model, cfg, cfg["batch"], 0, 1, None, "own")
+    times, e2e = measure_hot_path(torch, None, hp, stream, steps, max(args.warmup, 3), 1, e2e_argmax=True)
+    ms_step = median(times) / steps
+    tens = model_tensors(model)
+    by = float(sum(t.compressed_bytes for t in tens))
+    out["b16"] = {"workload": "mistral7b_b16", "what": cfg["desc"], "value": round(cfg["batch"] * 1e3 / ms_step, 1), "unit": "tok/s",
+                  "ms_per_step": round(ms_step, 4),
+                  "roofline": roofline_hbm(by / (ms_step * 1e-3) / 1e9, hbm_peak, peak_src, "gemm_stream_kernel", by,
+                                           TRAFFIC_RATIO.get("gemm_stream_kernel")),
+                  "e2e": e2e, "gpu_launches": hp.launches_per_step * steps * len(times),
+                  "timing_blocks_ms": {"n": len(times), "min": round(min(times), 3), "max": round(max(times), 3)}}
+    del hp
     torch.cuda.empty_cache()
 
     # ---- full_step: every kernel of the Mistral-7B-shaped decode step at B = 1

@@ -86,6 +86,31 @@ def test_every_cut_of_the_iteration_space(eng, O, monkeypatch, knobs, M, K, B):
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("B", [4, 16, 32])
+@pytest.mark.parametrize("whole", ["0", "1"])
+def test_multi_tensor_launch_qkv(eng, O, monkeypatch, B, whole):
+    """q/k/v-like tensors (own base_exp, own row counts, one ragged, one without escapes) as one launch: their row
+    tiles form one schedule."""
+    monkeypatch.setenv("S12_GSTREAM", "2")
+    monkeypatch.setenv("S12_GSTREAM_MAXB", "32")
+    monkeypatch.setenv("S12_GSTREAM_WHOLE", whole)
+    monkeypatch.setenv("S12_GSTREAM_MINIT", "3")
+    K = 1024
+    specs = [(512, 0.02, 1e-3), (130, 0.05, 5e-3), (128, 0.01, 0.0)]
+    ws, packs = [], []
+    for i, (M, std, frac) in enumerate(specs):
+        w = O.synth_weights(M, K, 200 + i, std=std, outlier_frac=frac)
+        ws.append(w); packs.append(O.pack(w))
+    x = O.synth_acts(B, K, 9)
+    outs = [torch.full((B, p.M + 4), float("nan"), device="cuda") for p in packs]
+    eng.gemm_multi([_cw(p) for p in packs], dev(x), outs, K, B)
+    torch.cuda.synchronize()
+    for w, p, o in zip(ws, packs, outs):
+        assert_close(o[:, :p.M], O.gemm_exact(w, x), what=f"M={p.M}")
+        assert torch.isnan(o[:, p.M:]).all()
+    assert eng.device_status() == 0
+
+
 def _tiny_exponent_weights(M, K, seed, escapes):
     rng = np.random.default_rng(seed)
     w = ((rng.integers(0, 2, (M, K)) << 15) | (rng.integers(1, 15, (M, K)) << 7) | rng.integers(0, 128, (M, K))).astype(np.uint16)

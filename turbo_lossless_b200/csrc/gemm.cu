@@ -87,6 +87,10 @@ int s12_gemm_multi_async(const S12Tensor* w, int num_tensors, const void* act, i
     }
     if (B == 0) return S12_OK;
     if (B < 0 || !act || act_stride < w[0].K) return fail(S12_ERR_BAD_ARG, "%s: B, act or act_stride", who);
+    if (B >= 2 && B <= 32) {                                      // the streaming kernel takes the tensors as one launch too
+        int rc = S12_OK;
+        if (gemm_stream_try(w, num_tensors, act, act_stride, outs, out_strides, B, stream, who, &rc) != 0) return rc;
+    }
     if (tc) return gemm_tc_launch_multi(w, num_tensors, act, act_stride, outs, out_strides, B, stream, who, nullptr);
     for (int i = 0; i < num_tensors; i++) {
         int rc = gemm_dispatch(&w[i], act, act_stride, outs[i], out_strides[i], B, stream, who);
