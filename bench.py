@@ -50,6 +50,8 @@ WORKLOADS = {
                          desc="Mistral-7B-shaped decode step at B=1 (BASELINE configs[1]): all split12 projections"),
     "mistral7b_b16": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=32000, batch=16,
                           desc="Mistral-7B-shaped decode step at B=16 (the engine's small-batch range): all split12 projections"),
+    "mistral7b_b32": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=32000, batch=32,
+                          desc="Mistral-7B-shaped decode step at B=32: all split12 projections"),
     "llama8b_b1": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=128256, batch=1,
                        desc="Llama-3.1-8B-shaped decode step at B=1: all split12 projections"),
     "llama8b_b256": dict(layers=32, hidden=4096, q=4096, kv=1024, ffn=14336, vocab=128256, batch=256,
