@@ -179,12 +179,16 @@ int s12_decompress_async(const S12Tensor* w, void* out_bf16, void* stream);
 int s12_gemv_async(const S12Tensor* w, int num_tensors, const void* act,
                    void* const* outs, void* stream);
 
-/* Small-batch GEMV, 1 <= B <= 16: out[b*out_stride + m], act[b*act_stride + k]. */
+/* Small-batch GEMV, 1 <= B <= 16: out[b*out_stride + m], act[b*act_stride + k].
+ * 2 <= B <= 16 on a tensor of 48 row tiles (6144 rows) or more runs the streaming
+ * mma.sync kernel, which borrows the GEMM workspace described at s12_gemm_async
+ * (same rule: calls of one device that may overlap must be serialised). */
 int s12_gemv_batched_async(const S12Tensor* w, const void* act, int act_stride,
                            void* out, int out_stride, int B, void* stream);
 
-/* Batched decode + GEMM, any B >= 1 (dispatches by B: the GEMV family for
- * B <= 16, the tensor-core kernel above; one kernel serves every B > 16).
+/* Batched decode + GEMM, any B >= 1 (dispatches by B: the streaming mma.sync
+ * kernel or the GEMV family for B <= 16, the tensor-core kernel above; one
+ * kernel serves every B > 16).
  * Exact escapes when w carries its CSR list.
  * All s12_gemm_* / nv_launch_split12_*gemm* calls of one device share one
  * partial-tile workspace (allocated by s12_init or by the first such call):
@@ -195,10 +199,11 @@ int s12_gemm_async(const S12Tensor* w, const void* act, int act_stride,
                    void* out, int out_stride, int B, void* stream);
 
 /* Up to four tensors that share K and the activations (q/k/v, gate/up) as ONE
- * tensor-core launch: their row tiles form one schedule, so small projections
+ * launch (the tensor-core kernel for B > 16, the streaming kernel for
+ * 2 <= B <= 16): their row tiles form one schedule, so small projections
  * (the 1024-row k and v of a GQA model) do not leave SMs idle.  outs[i] is fp32
- * [B][out_strides[i]].  Falls back to one s12_gemm_async per tensor when the
- * tensor-core path does not apply. */
+ * [B][out_strides[i]].  Falls back to one s12_gemm_async per tensor when
+ * neither kernel applies. */
 int s12_gemm_multi_async(const S12Tensor* w, int num_tensors, const void* act, int act_stride,
                          void* const* outs, const int* out_strides, int B, void* stream);
 
