@@ -25,11 +25,16 @@
 //     load phase then differ in bit 2 of the swizzle and the four rows of a 16-lane
 //     phase in bits 1-2, which makes both loads free of bank conflicts.
 //   * Escapes: the stream decodes an escape to the value the two-pass reference
-//     calls "wrong"; while the consumers stream a tile segment, the epilogue warps
-//     compute sum_p (correct_p - wrong_p) * x[col_p] over the segment's columns
-//     (second pass of the reference, nvidia_kernels.cu:271-290) from global memory
-//     and add it to the segment's sums, so the result is exact and the consumers
-//     never wait for global memory.
+//     calls "wrong"; while the consumers stream, the epilogue warps compute
+//     sum_p (correct_p - wrong_p) * x[col_p] over the rows' lists (second pass of
+//     the reference, nvidia_kernels.cu:271-290) and add it to the tile's sums, so
+//     the result is exact and the consumers never wait for global memory.  The
+//     32 rows of a pass own one contiguous piece of the CSR arrays, so the work
+//     is three rounds of independent loads (row offsets; columns and values,
+//     coalesced, into shared memory; one entry per lane, its activations of all
+//     sequences) followed by an in-order walk over shared memory.  A partial tile
+//     handed to another CTA carries no corrections; the CTA that finishes the
+//     tile adds the whole rows', and computes them before anything else.
 //   * At the end of a tile segment the 16 warps leave their accumulators in
 //     shared memory and go on; two epilogue warps add the four column quarters in
 //     a fixed order and store.  A tile cut by a range boundary is finished by its
@@ -149,7 +154,15 @@ gemm_stream_kernel(const __grid_constant__ SMaps maps, const __grid_constant__ C
     uint8_t* xs = raw + (size_t)P.raw_stages * kSRawBytes;
     float* part = reinterpret_cast<float*>(xs + kSXStages * kXStage);             // [quarter][row group][RPT][lane]
     float* corr_s = part + kSConsumers * RPT * 32;                                  // [epilogue warp][row group of the warp][RPT][lane]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(corr_s + kSEpiWarps * 2 * RPT * 32);
+    float* corr_o = corr_s + kSEpiWarps * 2 * RPT * 32;                             // the same for the tile finished for other CTAs
+    // escape entries of the 32 rows an epilogue warp is working on: column and correct - wrong, staged with coalesced
+    // loads, then every entry's products with the sequences' activations
+    constexpr int kStage = NB == 4 ? 0 : 128;                                      // entries per epilogue warp
+    constexpr int BB = 8 * NB;                                                     // sequences, padded
+    int* stg_col = reinterpret_cast<int*>(corr_o + kSEpiWarps * 2 * RPT * 32);
+    float* stg_dv = reinterpret_cast<float*>(stg_col + kSEpiWarps * kStage);
+    float* stg_prod = stg_dv + kSEpiWarps * kStage;                                // [entry][BB]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stg_prod + kSEpiWarps * kStage * BB);
     const uint32_t b_rawfull = smem_addr(bars);
     const uint32_t b_rawempty = b_rawfull + 8 * kSMaxRaw;
     const uint32_t b_xfull = b_rawempty + 8 * kSMaxRaw;
@@ -314,40 +327,76 @@ gemm_stream_kernel(const __grid_constant__ SMaps maps, const __grid_constant__ C
         const int g = lane >> 2, t4 = lane & 3;
         const int rho = ((g & 1) << 2) | (g & 2) | (g >> 2);
         grid_dependency_wait();                                  // the output buffer may still be in use
-        int nseg = 0;
-        for (int it = lo; it < hi;) {
-            const int tile = it / KB, kbs = it - tile * KB;
-            const int seg_len = min(KB - kbs, hi - it);
-            const bool starts = kbs == 0, ends = kbs + seg_len == KB;
+        // Escape corrections of a tile, sum_p (correct_p - wrong_p) * x[col_p] over the rows' whole lists, computed while
+        // the consumers stream and parked in shared memory in the accumulators' layout.  The walks are chains of
+        // dependent loads (row_off -> cols -> x), so they are started as early as possible: those of a whole tile when
+        // the epilogue reaches its segment (the segment then lasts a whole tile), those of the tile this CTA finishes
+        // for others -- the short last segment of a stream-K range -- before anything else.  Partial tiles handed to
+        // another CTA carry no corrections: the owner adds the whole rows'.
+        auto corrections = [&](int tile, float* buf) -> bool {
             const STile tr = s_locate(P, tile);
             const STensor& Tn = P.t[tr.ti];
-            // Escape corrections of the segment's columns, sum_p (correct_p - wrong_p) * x[col_p], computed while the
-            // consumers stream the segment and parked in shared memory in the accumulators' layout.
-            const bool has_corr = kMode != 1 && Tn.row_off != nullptr;
-            if (has_corr) {
-                const int k_lo = kbs * kSCols, k_hi = (kbs + seg_len) * kSCols;
+            if (kMode == 1 || Tn.row_off == nullptr) return false;
 #pragma unroll 1
-                for (int rl = 0; rl < 2; rl++) {
-                    float cr[RPT];
+            for (int rl = 0; rl < 2; rl++) {
+                float cr[RPT];
 #pragma unroll
-                    for (int j = 0; j < RPT; j++) cr[j] = 0.f;
-                    int p0[4], p1[4];
+                for (int j = 0; j < RPT; j++) cr[j] = 0.f;
+                // The 32 rows' entries are one contiguous piece of the CSR arrays.  Three rounds of independent loads
+                // instead of a chain per entry: the rows' offsets (one per lane); the head of the piece (columns and
+                // values, coalesced) into shared memory; every staged entry's activations of all sequences, whose
+                // products with the entry's value are parked in shared memory too.  The walk over the rows then adds
+                // the products in entry order (deterministic) and goes to global memory only past the staged head.
+                const int m0 = tr.mt * kSRows + (2 * e + rl) * 32;
+                int* scol = stg_col + e * kStage;
+                float* sdv = stg_dv + e * kStage;
+                float* sprod = stg_prod + e * kStage * BB;
+                const int ro = Tn.row_off[min(m0 + lane, Tn.M)];             // row_off has M + 1 entries
+                const int ro_end = Tn.row_off[min(m0 + 32, Tn.M)];
+                const int P0 = __shfl_sync(0xFFFFFFFFu, ro, 0);
+                const int nst = min(ro_end - P0, kStage);
+                __syncwarp();                                    // the previous pass has finished reading the staging area
+                for (int i = lane; i < nst; i += 32) {
+                    float dv = bf16_bits_to_float((uint16_t)Tn.correct[P0 + i]);
+                    if (kMode == 0) dv -= bf16_bits_to_float((uint16_t)Tn.wrong[P0 + i]);
+                    scol[i] = Tn.cols[P0 + i];
+                    sdv[i] = dv;
+                }
+                __syncwarp();
+                // a lane takes an entry and loads its column's activation of every sequence: the loads of a round are
+                // independent, and the lanes of one load instruction read the same activation row (measured: with the
+                // sequences spread over the lanes instead, the same loads took three times as long)
+                for (int e0 = 0; e0 < nst; e0 += 32) {
+                    const int en = e0 + lane;
+                    const int col = en < nst ? scol[en] : 0;
+                    float xv[BB];
 #pragma unroll
-                    for (int r = 0; r < 4; r++) {
-                        const int m = tr.mt * kSRows + (2 * e + rl) * 32 + (r >> 1) * 16 + (r & 1) * 8 + rho;
-                        p0[r] = p1[r] = 0;
-                        if (m < Tn.M) { p0[r] = Tn.row_off[m]; p1[r] = Tn.row_off[m + 1]; }
+                    for (int b2 = 0; b2 < BB; b2++)
+                        xv[b2] = b2 < P.B ? bf16_bits_to_float(__ldg(P.x + (size_t)b2 * P.x_stride + col)) : 0.f;
+                    if (en < nst) {
+                        const float dv = sdv[en];
+#pragma unroll
+                        for (int b2 = 0; b2 < BB; b2++) sprod[en * BB + b2] = dv * xv[b2];
                     }
-                    // the four rows' lists are walked in lockstep, so that their loads overlap
-                    int longest = max(max(p1[0] - p0[0], p1[1] - p0[1]), max(p1[2] - p0[2], p1[3] - p0[3]));
-                    longest = __reduce_max_sync(0xFFFFFFFFu, longest);
-                    for (int t = 0; t < longest; t++) {
+                }
+                __syncwarp();
 #pragma unroll
-                        for (int r = 0; r < 4; r++) {
-                            const int p = p0[r] + t;
-                            if (p >= p1[r]) continue;
+                for (int r = 0; r < 4; r++) {
+                    const int rr = (r >> 1) * 16 + (r & 1) * 8 + rho;   // row within the 32
+                    const int q0 = __shfl_sync(0xFFFFFFFFu, ro, rr);
+                    const int qn = __shfl_sync(0xFFFFFFFFu, ro, (rr + 1) & 31);
+                    const int q1 = rr == 31 ? ro_end : qn;
+                    for (int p = q0; p < q1; p++) {
+                        if (p - P0 < nst) {
+                            const float* pr = sprod + (p - P0) * BB + 2 * t4;
+#pragma unroll
+                            for (int i = 0; i < NB; i++) {
+                                const float2 c2 = *reinterpret_cast<const float2*>(pr + 8 * i);
+                                cr[((r >> 1) * NB + i) * 4 + (r & 1) * 2 + 0] += c2.x;
+                                cr[((r >> 1) * NB + i) * 4 + (r & 1) * 2 + 1] += c2.y;
+                            }
+                        } else {
                             const int col = Tn.cols[p];
-                            if (col < k_lo || col >= k_hi) continue;
                             float dv = bf16_bits_to_float((uint16_t)Tn.correct[p]);
                             if (kMode == 0) dv -= bf16_bits_to_float((uint16_t)Tn.wrong[p]);
 #pragma unroll
@@ -360,17 +409,33 @@ gemm_stream_kernel(const __grid_constant__ SMaps maps, const __grid_constant__ C
                             }
                         }
                     }
-                    float* dstc = corr_s + (size_t)((e * 2 + rl) * RPT) * 32 + lane;
-#pragma unroll
-                    for (int j = 0; j < RPT; j++) dstc[j * 32] = cr[j];
                 }
+                float* dstc = buf + (size_t)((e * 2 + rl) * RPT) * 32 + lane;
+#pragma unroll
+                for (int j = 0; j < RPT; j++) dstc[j * 32] = cr[j];
             }
+            return true;
+        };
+        const int tile_last = (hi - 1) / KB;
+        const bool owner_last = max(lo, tile_last * KB) == tile_last * KB && hi < (tile_last + 1) * KB;
+        const bool owner_corr = owner_last ? corrections(tile_last, corr_o) : false;
+        int nseg = 0;
+        for (int it = lo; it < hi;) {
+            const int tile = it / KB, kbs = it - tile * KB;
+            const int seg_len = min(KB - kbs, hi - it);
+            const bool starts = kbs == 0, ends = kbs + seg_len == KB;
+            const STile tr = s_locate(P, tile);
+            const STensor& Tn = P.t[tr.ti];
+            bool has_corr = false;
+            const float* cbuf = corr_s;
+            if (starts && ends) has_corr = corrections(tile, corr_s);
+            else if (starts) { has_corr = owner_corr; cbuf = corr_o; }
             if (!mbar_wait(b_pready, (uint32_t)nseg & 1, P.status, 0x80000u, &s_abort)) break;
             float v[2][RPT];
 #pragma unroll
             for (int rl = 0; rl < 2; rl++) {
                 const float* src = part + (size_t)((2 * e + rl) * RPT) * 32 + lane;
-                const float* srcc = corr_s + (size_t)((e * 2 + rl) * RPT) * 32 + lane;
+                const float* srcc = cbuf + (size_t)((e * 2 + rl) * RPT) * 32 + lane;
 #pragma unroll
                 for (int j = 0; j < RPT; j++) {
                     const float q0 = src[j * 32], q1 = src[(4 * RPT + j) * 32];
@@ -430,7 +495,8 @@ gemm_stream_kernel(const __grid_constant__ SMaps maps, const __grid_constant__ C
 static size_t stream_smem_bytes(int NB, int raw_stages)
 {
     return 1024 + (size_t)raw_stages * kSRawBytes + (size_t)kSXStages * 4 * (8 * NB * 128) +
-           (size_t)(kSConsumers + 2 * kSEpiWarps) * 8 * NB * 32 * sizeof(float) + kSNumBars * 8;
+           (size_t)(kSConsumers + 4 * kSEpiWarps) * 8 * NB * 32 * sizeof(float) + (size_t)kSEpiWarps * (NB == 4 ? 0 : 128) * (8 + 4 * 8 * NB) +
+           kSNumBars * 8;
 }
 
 typedef void (*SKern)(const SMaps, const CUtensorMap, const SParams);
@@ -462,9 +528,11 @@ int gemm_stream_try(const S12Tensor* w, int nt, const void* act, int act_stride,
         weights += (long long)s.M * K;
     }
     if (neg && K % kSCols != 0) return 0;                         // columns past K decode to infinities in that mode
-    // Fewer than 48 row tiles: a third of the SMs or less would hold whole tiles, and the stream-K cut pays its
-    // hand-over on a launch of 10-20 us; measured, the register-pipelined GEMV family is faster there.
-    if (weights < 48ll * kSRows * K && use != 2) return 0;
+    // Small tensors: a third of the SMs or less would hold whole tiles, and the stream-K cut pays its hand-over on
+    // a launch of 10-20 us.  Measured against the register-pipelined GEMV family: up to 8 sequences that family
+    // wins below 48 row tiles; from 9 to 16 (where it runs its 16-wide form) below ~24 M weights.
+    const long long min_weights = B <= 8 ? 48ll * kSRows * K : (24ll << 20);
+    if (weights < min_weights && use != 2) return 0;
     if (!tma_available()) return 0;
     // one decode mode per launch: a window starting at exponent zero anywhere selects the slow forms
     const int mode = !neg ? 0 : (csr_any ? 2 : 1);
@@ -552,9 +620,7 @@ int gemm_stream_try(const S12Tensor* w, int nt, const void* act, int act_stride,
     const double t_c = NB == 4 ? 1.7 : 0.9, hbm_bytes_per_us = 5.9e6, fixup_us = 3.0;
     auto stage_us = [&](int G) { return std::max(t_c, (double)kSRawBytes * G / hbm_bytes_per_us); };
     int grid = (int)std::min<long long>(cap, std::max<long long>(1, T / per));
-    // with escape lists, the corrections of the short segments of a stream-K cut are not hidden: ~7 us per 4096 columns
-    const double corr_us = csr_any ? 7.0 * K / 4096.0 : 0.0;
-    const double t_sk = ((double)T / grid) * stage_us(grid) + (grid > 1 ? fixup_us + corr_us : 0.0);
+    const double t_sk = ((double)T / grid) * stage_us(grid) + (grid > 1 ? fixup_us : 0.0);
     const int rounds = (mtiles + cap - 1) / cap;
     const int g_whole = (mtiles + rounds - 1) / rounds;
     const double t_whole = (double)rounds * P.KB * stage_us(g_whole);
