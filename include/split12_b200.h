@@ -249,7 +249,11 @@ const char* s12_last_error(void);
 /* Library version: major*10000 + minor*100 + patch. */
 int s12_version(void);
 /* Reads and clears the device-side status word of the current device
- * (0 = ok; non-zero = a bounded wait expired; bits name the site), including
+ * (0 = ok; non-zero = a bounded wait expired; bits name the site: 0x1-0x8 the
+ * streaming GEMV's copy, consumer, reduction and epilogue waits, 0x10-0x4000
+ * the tensor-core GEMM's roles, 0x8000 a peer wait of the all-reduce,
+ * 0x10000-0x80000 the streaming small-batch kernel's weight copies,
+ * activation copies, consumers and epilogue / hand-over), including
  * the word of s12_gemm_noalloc_async.  When it was non-zero the GEMM's
  * hand-over counters are zeroed again, so later launches start clean.
  * Synchronises the device. */
