@@ -38,6 +38,34 @@ def test_emulated_ranks_one_launch(world, n):
         c.close()
 
 
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("n", [16388, 65536 + 8, 100004])
+def test_two_shot_form(monkeypatch, world, n):
+    """Reduce-scatter + all-gather inside one kernel (large vectors, four ranks or more by default; forced here for
+    every world): the sums are added in rank order by the part's owner, so they carry the same bits as the one-shot
+    form, on every rank; consecutive calls alternate the areas; parts of a slice that do not divide evenly."""
+    import torch
+    from turbo_lossless_b200 import TPComm, Split12Engine
+    monkeypatch.setenv("S12_COMM_TWOSHOT", "1")
+    eng = Split12Engine()
+    comms = TPComm.local(world, 300000)
+    rng = np.random.default_rng(world * 7 + n)
+    for call in range(3):
+        parts = [rng.standard_normal(n).astype(np.float32) for _ in range(world)]
+        srcs = [torch.from_numpy(p).cuda() for p in parts]
+        dsts = [torch.full((n,), float("nan"), device="cuda") for _ in range(world)]
+        TPComm.all_reduce_emulated(comms, srcs, dsts)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        ref = np.zeros(n, dtype=np.float32)
+        for p in parts:
+            ref = ref + p
+        for d in dsts:
+            np.testing.assert_array_equal(d.cpu().numpy(), ref)
+    for c in comms:
+        c.close()
+
+
 def test_rejects_bad_sizes():
     import torch
     from turbo_lossless_b200 import TPComm, S12Error
@@ -199,7 +227,9 @@ from turbo_lossless_b200 import TPComm, Split12Engine
 eng = Split12Engine()
 comm = TPComm(rank, world, 1 << 20)
 ok = True
-for call, n in enumerate([4096, 4096, 14336, 1 << 20, 4096]):
+for call, n in enumerate([4096, 4096, 14336, 1 << 20, 4096, 1 << 20, 65544, 20000, 4096]):
+    if call == 5:
+        os.environ["S12_COMM_TWOSHOT"] = "1"                 # the reduce-scatter + all-gather form from here on
     parts = [np.random.default_rng(100 * call + r).standard_normal(n).astype(np.float32) for r in range(world)]
     x = torch.from_numpy(parts[rank]).cuda()
     out = torch.empty_like(x)
@@ -209,6 +239,7 @@ for call, n in enumerate([4096, 4096, 14336, 1 << 20, 4096]):
     for p in parts:
         ref = ref + p
     ok = ok and np.array_equal(out.cpu().numpy(), ref) and eng.device_status() == 0
+os.environ.pop("S12_COMM_TWOSHOT", None)
 # row-parallel GEMV fused with its all-reduce: each rank holds a column slice of W
 from oracle import oracle as O
 from turbo_lossless_b200 import CompressedWeight

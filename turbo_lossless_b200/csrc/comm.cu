@@ -7,8 +7,9 @@
 // its own memory that all ranks can address (CUDA IPC; the handles travel
 // through the caller's process group):
 //
-//   recv  [2 parities][world][capacity] fp32   partial vectors, one row per source rank
-//   flags [2 parities][kMaxCtas][world] u32    arrival tokens, one per (CTA, source rank)
+//   recv   [2 parities][world][capacity] fp32            partial vectors, one row per source rank
+//   flags  [2 phases][2 parities][kMaxCtas][world] u32   arrival tokens, one per (CTA, source rank)
+//   gather [2 parities][capacity] fp32                   reduced slices (two-shot form)
 //
 // One-shot algorithm, per CTA on its own slice of the vector (so no grid-wide
 // step exists): push the slice into every rank's recv[parity][my rank], fence,
@@ -71,6 +72,64 @@ allreduce_kernel(const __grid_constant__ AllReduceParams P)
     if (threadIdx.x == 0) comm_retire(R, token, gridDim.x);
 }
 
+// Two-shot form for large vectors on four or more ranks.  The one-shot kernel above sends every element to every
+// rank: (world - 1) x n floats leave each GPU.  Here a CTA cuts its slice into `world` parts; part j of every rank is
+// pushed to rank j only (reduce-scatter), rank j adds the world partials of its part in rank order -- the same order
+// and therefore the same bits as the one-shot form -- and pushes the sums into every rank's gather area (all-gather),
+// from where each rank copies its slice out: 2 x (world - 1) / world x n floats leave each GPU, 3.5 x less on eight
+// ranks, at the price of a second signal-and-wait round.  Same parities, same call counter.
+__global__ void __launch_bounds__(kCommThreads)
+allreduce_twoshot_kernel(const __grid_constant__ AllReduceParams P)
+{
+    const CommRank& R = P.r[blockIdx.y];
+    const float* in = P.in[blockIdx.y];
+    float* out = P.out[blockIdx.y];
+    const int world = P.world, me = R.rank, cta = blockIdx.x;
+    if (P.early_trigger) grid_launch_dependents();
+    grid_dependency_wait();
+    int parity;
+    const unsigned int token = comm_begin(R, parity);
+    const int n4 = P.n >> 2;
+    const int lo = (int)((long long)n4 * cta / gridDim.x), hi = (int)((long long)n4 * (cta + 1) / gridDim.x);
+    const int len = hi - lo;
+    const size_t row = (size_t)P.capacity;
+    auto part_lo = [&](int j) { return lo + (int)((long long)len * j / world); };
+
+    // reduce-scatter: part j of my slice goes to rank j's receive row for me
+#pragma unroll 1
+    for (int j = 0; j < world; j++) {
+        float4* dst = reinterpret_cast<float4*>(R.recv[j] + ((size_t)parity * world + me) * row);
+        for (int i = part_lo(j) + threadIdx.x; i < part_lo(j + 1); i += kCommThreads)
+            dst[i] = reinterpret_cast<const float4*>(in)[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    comm_signal_and_wait(R, world, parity, cta, token, threadIdx.x, 0);
+    __syncthreads();
+    // my part: add the partials in rank order, send the sums to every rank's gather area
+    const float* mine = R.recv[me] + (size_t)parity * world * row;
+    for (int i = part_lo(me) + threadIdx.x; i < part_lo(me + 1); i += kCommThreads) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+        for (int p = 0; p < world; p++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(mine + p * row) + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+#pragma unroll 1
+        for (int q = 0; q < world; q++)
+            reinterpret_cast<float4*>(R.gather[q] + (size_t)parity * row)[i] = acc;
+    }
+    __threadfence_system();
+    __syncthreads();
+    comm_signal_and_wait(R, world, parity, cta, token, threadIdx.x, 1);
+    __syncthreads();
+    if (!P.early_trigger) grid_launch_dependents();
+    const float4* g = reinterpret_cast<const float4*>(R.gather[me] + (size_t)parity * row);
+    for (int i = lo + threadIdx.x; i < hi; i += kCommThreads) reinterpret_cast<float4*>(out)[i] = __ldcg(g + i);
+    __syncthreads();
+    if (threadIdx.x == 0) comm_retire(R, token, gridDim.x);
+}
+
 // Small vectors (a B = 1 hidden state is 16 KB): latency is everything, so value and arrival token travel
 // in ONE 8-byte word.  A rank stores {bits, token} of each of its elements into every rank's area and then
 // polls, element by element, the words the other ranks stored for it: no fence, no separate flag, no
@@ -129,7 +188,7 @@ struct S12Comm {
     int rank = 0, world = 1, device = 0;
     int capacity = 0;                         // floats per receive row
     char* base = nullptr;                     // local allocation: recv area, then flag area
-    size_t recv_bytes = 0, flag_bytes = 0, ll_bytes = 0;
+    size_t recv_bytes = 0, flag_bytes = 0, ll_bytes = 0, gather_bytes = 0;
     char* peer_base[s12::kCommMaxWorld] = {};  // every rank's allocation as mapped in this process
     bool opened[s12::kCommMaxWorld] = {};      // mapped through an IPC handle (must be closed)
     unsigned int* calls = nullptr;             // [0] calls completed, [1] CTAs done in the running call
@@ -155,10 +214,11 @@ int s12_comm_create(int rank, int world, long long max_floats, S12Comm** out, vo
     int rc = check_cuda(cudaGetDevice(&c->device), who);
     c->recv_bytes = (size_t)2 * world * c->capacity * sizeof(float);
     c->recv_bytes = (c->recv_bytes + 255) & ~(size_t)255;
-    c->flag_bytes = (size_t)2 * kCommMaxCtas * world * sizeof(unsigned int);
+    c->flag_bytes = (size_t)2 * 2 * kCommMaxCtas * world * sizeof(unsigned int);     // two phases x two parities
     c->flag_bytes = (c->flag_bytes + 255) & ~(size_t)255;
     c->ll_bytes = (size_t)2 * world * kCommLLMax * sizeof(unsigned long long);
-    const size_t total = c->recv_bytes + c->flag_bytes + c->ll_bytes;
+    c->gather_bytes = (size_t)2 * c->capacity * sizeof(float);
+    const size_t total = c->recv_bytes + c->flag_bytes + c->ll_bytes + c->gather_bytes;
     if (!rc) rc = check_cuda(cudaMalloc(&c->base, total), who);
     if (!rc) rc = check_cuda(cudaMemset(c->base, 0, total), who);
     if (!rc) rc = check_cuda(cudaMalloc(&c->calls, 2 * sizeof(unsigned int)), who);
@@ -218,12 +278,23 @@ static int fill_rank(const S12Comm* c, s12::CommRank& R)
         R.recv[p] = reinterpret_cast<float*>(c->peer_base[p]);
         R.flags[p] = reinterpret_cast<unsigned int*>(c->peer_base[p] + c->recv_bytes);
         R.ll[p] = reinterpret_cast<unsigned long long*>(c->peer_base[p] + c->recv_bytes + c->flag_bytes);
+        R.gather[p] = reinterpret_cast<float*>(c->peer_base[p] + c->recv_bytes + c->flag_bytes + c->ll_bytes);
     }
     R.calls = c->calls;
     R.status = s12::device_status_word();
     R.wait_ns = c->wait_ns;
     R.rank = c->rank;
     return R.status ? S12_OK : S12_ERR_CUDA;
+}
+
+// Two-shot form: four ranks or more and vectors from 64 K floats up (tuning knob S12_COMM_TWOSHOT: -1 this rule, 0 never,
+// 1 whenever the vector is not a small message).
+static bool use_twoshot(int world, int n)
+{
+    const int k = s12::env_knob("S12_COMM_TWOSHOT", -1);
+    if (k == 0 || world < 2) return false;
+    if (k > 0) return true;
+    return world >= 4 && n >= 65536;
 }
 
 static int comm_ctas(int n)
@@ -254,6 +325,8 @@ int s12_allreduce_f32_async(S12Comm* c, const void* in, void* out, int n, void* 
         ctas = ctas > 16 ? 16 : ctas;
         return launch(allreduce_ll_kernel, dim3(ctas, 1), dim3(256), 0, stream, who, P);
     }
+    if (use_twoshot(c->world, n))
+        return launch(allreduce_twoshot_kernel, dim3(comm_ctas(n), 1), dim3(kCommThreads), 0, stream, who, P);
     return launch(allreduce_kernel, dim3(comm_ctas(n), 1), dim3(kCommThreads), 0, stream, who, P);
 }
 
@@ -276,10 +349,12 @@ int s12_allreduce_f32_emulated_async(S12Comm* const* comms, int world, const voi
     const bool small = n <= kCommLLMax && env_knob("S12_COMM_LL", 1);
     const int ctas = small ? std::min(16, (n + 1023) / 1024) : comm_ctas(n);
     const int threads = small ? 256 : kCommThreads;
-    const void* kern = small ? (const void*)allreduce_ll_kernel : (const void*)allreduce_kernel;
+    const bool two = !small && use_twoshot(world, n);
+    const void* kern = small ? (const void*)allreduce_ll_kernel : (two ? (const void*)allreduce_twoshot_kernel : (const void*)allreduce_kernel);
     int per_sm = 0;
     int rc = check_cuda(small ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_ll_kernel, threads, 0)
-                              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_kernel, threads, 0), who);
+                              : (two ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_twoshot_kernel, threads, 0)
+                                     : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_kernel, threads, 0)), who);
     if (rc) return rc;
     if ((long long)ctas * world > (long long)per_sm * sm_count())
         return fail(S12_ERR_TOO_LARGE, "%s: %d x %d CTAs cannot be resident together", who, ctas, world);
@@ -301,7 +376,7 @@ int s12_comm_reset(S12Comm* c)
     const char* who = "s12_comm_reset";
     if (!c) return fail(S12_ERR_BAD_ARG, "%s: null communicator", who);
     int rc = check_cuda(cudaDeviceSynchronize(), who);
-    if (!rc) rc = check_cuda(cudaMemset(c->base, 0, c->recv_bytes + c->flag_bytes + c->ll_bytes), who);
+    if (!rc) rc = check_cuda(cudaMemset(c->base, 0, c->recv_bytes + c->flag_bytes + c->ll_bytes + c->gather_bytes), who);
     if (!rc) rc = check_cuda(cudaMemset(c->calls, 0, 2 * sizeof(unsigned int)), who);
     if (!rc) rc = check_cuda(cudaDeviceSynchronize(), who);
     return rc;

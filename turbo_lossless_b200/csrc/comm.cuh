@@ -30,6 +30,7 @@ struct CommRank {
     float* recv[kCommMaxWorld];              // every rank's receive area (index = owner rank), as mapped here
     unsigned int* flags[kCommMaxWorld];      // every rank's flag area
     unsigned long long* ll[kCommMaxWorld];   // every rank's small-message area: 8-byte words {value bits, token}
+    float* gather[kCommMaxWorld];            // every rank's area for reduced slices (two-shot form): [2 parities][capacity]
     unsigned int* calls;                     // local: [0] collective calls completed, [1] CTAs of the running call that are done
     unsigned int* status;                    // local status word (bit 0x8000: a wait gave up)
     unsigned long long wait_ns;              // how long a wait for a peer may last (s12_comm_set_wait_limit_ms)
@@ -62,16 +63,18 @@ __device__ __forceinline__ unsigned int comm_begin(const CommRank& R, int& parit
     parity = (int)(calls & 1u);
     return calls + 1u;
 }
-__device__ __forceinline__ size_t comm_flag_index(int parity, int cta, int world, int src)
+// phase 0: the partials have been pushed; phase 1 (two-shot form): the reduced slices have been pushed
+__device__ __forceinline__ size_t comm_flag_index(int parity, int cta, int world, int src, int phase = 0)
 {
-    return ((size_t)parity * kCommMaxCtas + cta) * world + src;
+    return (((size_t)phase * 2 + parity) * kCommMaxCtas + cta) * world + src;
 }
 // threads 0..world-1 of the calling group signal and then wait; `tid` is the index inside the group
-__device__ __forceinline__ void comm_signal_and_wait(const CommRank& R, int world, int parity, int cta, unsigned int token, int tid)
+__device__ __forceinline__ void comm_signal_and_wait(const CommRank& R, int world, int parity, int cta, unsigned int token, int tid,
+                                                     int phase = 0)
 {
     if (tid < world) {
-        st_release_sys(R.flags[tid] + comm_flag_index(parity, cta, world, R.rank), token);
-        const unsigned int* f = R.flags[R.rank] + comm_flag_index(parity, cta, world, tid);
+        st_release_sys(R.flags[tid] + comm_flag_index(parity, cta, world, R.rank, phase), token);
+        const unsigned int* f = R.flags[R.rank] + comm_flag_index(parity, cta, world, tid, phase);
         unsigned long long t0 = 0;
         while ((int)(ld_acquire_sys(f) - token) < 0) {
             const unsigned long long now = global_time_ns();
