@@ -7,8 +7,10 @@
 // weights whatever B is.  Here the decoded weights never leave the registers:
 //
 //   * Persistent CTAs, one per SM, 20 warps.  The work is the list of
-//     (row tile of 128 rows, raw stage of 256 columns) iterations, cut into equal
-//     contiguous ranges (stream-K), so every SM streams the same number of bytes.
+//     (row tile of 128 rows, raw stage of 256 columns) iterations, cut either into
+//     equal contiguous ranges (stream-K: every SM streams the same number of
+//     bytes) or into ranges of whole tiles (no hand-over between CTAs); a small
+//     cost model on the host picks.
 //   * A producer thread fetches a raw stage as three TMA boxes (two 128 B x 128
 //     row boxes of sm, one of gr, 128-byte swizzle) into a ring; a second one
 //     fetches the activations of the stage's 256 columns for all sequences (four
