@@ -41,7 +41,7 @@ __device__ __forceinline__ void patch_escapes8(uint32_t g, int64_t elem0, int ro
     }
 }
 
-// Fast path: K % 16 == 0.  kChunks chunks of 16 elements per thread.
+// Fast path: K % 16 == 0.  kChunks chunks of 16 elements per thread (the launcher uses one).
 template <int kMode, int kChunks>
 __global__ void __launch_bounds__(256)
 decompress16_kernel(const uint8_t* __restrict__ sm, const uint8_t* __restrict__ gr, uint32_t base2,
@@ -121,7 +121,9 @@ extern "C" int s12_decompress_async(const S12Tensor* w, void* out_bf16, void* st
     int64_t n = (int64_t)w->M * w->K;
     if ((w->K % 16) == 0 && (reinterpret_cast<uintptr_t>(w->sm) % 16) == 0 &&
         (reinterpret_cast<uintptr_t>(w->gr) % 8) == 0 && (reinterpret_cast<uintptr_t>(out_bf16) % 16) == 0) {
-        constexpr int kChunks = 4;
+        // one chunk per thread: a CTA then reads 4 KB + 2 KB and writes 8 KB, all contiguous; measured 6.19 TB/s
+        // against 5.85 / 5.71 / 4.97 TB/s with 2 / 4 / 8 chunks per thread (whose chunks lie 4 KB apart)
+        constexpr int kChunks = 1;
         int64_t chunks = n / 16;
         int64_t blocks = (chunks + 256 * kChunks - 1) / (256 * kChunks);
         if (blocks > 0x7FFFFFFF) return fail(S12_ERR_TOO_LARGE, "s12_decompress_async: tensor too large");
