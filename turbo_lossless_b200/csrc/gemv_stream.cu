@@ -496,6 +496,10 @@ int gemv_stream_try(const S12Tensor* w, int nt, const void* act, void* const* ou
     // and the shared memory the fourth stages would take stays with the L1 that serves the epilogue's
     // escape lists and the activation staging.
     int depth = (ctas == 2 && fit > 3) ? 3 : fit;
+    // Small tensors (a CTA streams four tiles or fewer): two stages.  Measured on 4096 x 4096 tensors, 8.3 -> 7.7 us
+    // per launch; on tensors with more tiles per CTA the third stage is worth 2 %.
+    const int small_tiles = env_knob("S12_GEMV_SMALL", 4);
+    if (ctas == 2 && depth > 2 && (long long)blocks * P.tpr <= (long long)small_tiles * sms * ctas) depth = 2;
     if (force_depth >= 2) depth = force_depth < fit ? force_depth : fit;
     P.depth = depth;
     const size_t smem = fixed + (size_t)depth * kStageBytes;
