@@ -47,6 +47,7 @@
 #include "common.cuh"
 #include <cuda.h>
 #include <algorithm>
+#include <cmath>
 #include <mutex>
 
 namespace s12 {
@@ -612,20 +613,33 @@ int gemm_stream_try(const S12Tensor* w, int nt, const void* act, int act_stride,
         }
     }
     // How the iteration space is cut.  Stream-K gives every CTA the same number of raw stages but most tiles are
-    // then finished through the workspace (~3 us at the end of the owners' ranges); whole tiles need no hand-over
-    // but leave SMs idle or unevenly loaded.  A small model in microseconds picks: a stage costs the larger of
-    // the consumers' time (measured: ~0.9 us up to 16 sequences, ~1.7 us above) and the stage's share of HBM
-    // time when G CTAs stream at once.
+    // then finished through the workspace (~3 us at the end of the owners' ranges) and every tile segment of a CTA
+    // costs an exchange through shared memory and an epilogue pass (~1.5 us); whole tiles need no hand-over but
+    // leave SMs idle or unevenly loaded.  Between the two: stream-K with a CTA count that cuts every tile at the
+    // same places (the range length divides the tile's stages), so that a CTA has one segment and an owner one
+    // contributor list of equal parts.  A small model in microseconds picks: a stage costs the larger of the
+    // consumers' time (measured: ~0.9 us up to 16 sequences, ~1.7 us above) and the stage's share of HBM time when
+    // G CTAs stream at once.
     const int sms = sm_count();
     const int per = std::max(1, env_knob("S12_GSTREAM_MINIT", 4));       // raw stages per CTA, at least (stream-K)
     const int cap = std::max(1, std::min(sms, env_knob("S12_GSTREAM_MAXGRID", sms)));
-    const double t_c = NB == 4 ? 1.7 : 0.9, hbm_bytes_per_us = 5.9e6, fixup_us = 3.0;
+    const double t_c = NB == 4 ? 1.7 : 0.9, hbm_bytes_per_us = 5.9e6, fixup_us = 3.0, seg_us = 1.5;
     auto stage_us = [&](int G) { return std::max(t_c, (double)kSRawBytes * G / hbm_bytes_per_us); };
     int grid = (int)std::min<long long>(cap, std::max<long long>(1, T / per));
-    const double t_sk = ((double)T / grid) * stage_us(grid) + (grid > 1 ? fixup_us : 0.0);
+    const double len_sk = (double)T / grid;
+    double t_sk = len_sk * stage_us(grid) + (grid > 1 ? fixup_us : 0.0) + seg_us * (1.0 + std::ceil(len_sk / P.KB));
+    // the largest CTA count whose ranges cut every tile into equal parts
+    for (int G = grid; G >= 1; G--) {
+        if (T % G) continue;
+        const long long L = T / G;
+        if (L < per || L >= P.KB || P.KB % L) continue;
+        const double t = (double)L * stage_us(G) + fixup_us + seg_us;
+        if (t < t_sk) { t_sk = t; grid = G; }
+        break;
+    }
     const int rounds = (mtiles + cap - 1) / cap;
     const int g_whole = (mtiles + rounds - 1) / rounds;
-    const double t_whole = (double)rounds * P.KB * stage_us(g_whole);
+    const double t_whole = (double)rounds * P.KB * stage_us(g_whole) + seg_us * rounds;
     const int sched = env_knob("S12_GSTREAM_WHOLE", -1);                 // tuning knob: -1 model, 0 stream-K, 1 whole tiles
     P.whole = sched < 0 ? (t_whole <= t_sk) : (sched != 0);
     if (P.whole) grid = g_whole;
