@@ -180,9 +180,10 @@ int s12_gemv_async(const S12Tensor* w, int num_tensors, const void* act,
                    void* const* outs, void* stream);
 
 /* Small-batch GEMV, 1 <= B <= 16: out[b*out_stride + m], act[b*act_stride + k].
- * 2 <= B <= 16 on a tensor of 48 row tiles (6144 rows) or more runs the streaming
- * mma.sync kernel, which borrows the GEMM workspace described at s12_gemm_async
- * (same rule: calls of one device that may overlap must be serialised). */
+ * 2 <= B <= 16 on a large tensor (8192 rows or more; from 9 sequences: 24 M
+ * weights or more) runs the streaming mma.sync kernel, which borrows the GEMM
+ * workspace described at s12_gemm_async (same rule: calls of one device that
+ * may overlap must be serialised). */
 int s12_gemv_batched_async(const S12Tensor* w, const void* act, int act_stride,
                            void* out, int out_stride, int B, void* stream);
 

@@ -1,5 +1,5 @@
 """The streaming small-batch kernel (gemm_stream.cu) behind s12_gemv_batched_async and s12_gemm_async, against the
-oracle.  By default it takes 2 <= B <= 16 on tensors of 48 row tiles or more; S12_GSTREAM=2 forces it on smaller
+oracle.  By default it takes 2 <= B <= 8 on tensors of 64 row tiles or more and 9 <= B <= 16 on 24 M weights or more; S12_GSTREAM=2 forces it on smaller
 shapes, S12_GSTREAM_MAXB=32 on 17..32 sequences (its four-column-tile form), S12_GSTREAM=0 turns it off (the kernels
 that serve those cases otherwise are the second opinion)."""
 import numpy as np
@@ -161,8 +161,8 @@ def test_without_the_escape_list_escapes_stay_wrong(eng, O, monkeypatch, B):
 
 
 def test_default_dispatch_takes_large_tensors(eng, O):
-    """No knobs: 7000 x 4096 at B = 8 (55 row tiles) goes through the streaming kernel, and is exact."""
-    M, K, B = 7000, 4096, 8
+    """No knobs: 9000 x 4096 at B = 8 (71 row tiles) goes through the streaming kernel, and is exact."""
+    M, K, B = 9000, 4096, 8
     w = O.synth_weights(M, K, 11, outlier_frac=1e-3)
     p = O.pack(w)
     x = O.synth_acts(B, K, 3)

@@ -533,8 +533,9 @@ int gemm_stream_try(const S12Tensor* w, int nt, const void* act, int act_stride,
     if (neg && K % kSCols != 0) return 0;                         // columns past K decode to infinities in that mode
     // Small tensors: a third of the SMs or less would hold whole tiles, and the stream-K cut pays its hand-over on
     // a launch of 10-20 us.  Measured against the register-pipelined GEMV family: up to 8 sequences that family
-    // wins below 48 row tiles; from 9 to 16 (where it runs its 16-wide form) below ~24 M weights.
-    const long long min_weights = B <= 8 ? 48ll * kSRows * K : (24ll << 20);
+    // wins below 64 row tiles (below 48 when the call holds several tensors, which it would serve one launch
+    // each); from 9 to 16 (where it runs its 16-wide form) below ~24 M weights.
+    const long long min_weights = B <= 8 ? (nt == 1 ? 64ll : 48ll) * kSRows * K : (24ll << 20);
     if (weights < min_weights && use != 2) return 0;
     if (!tma_available()) return 0;
     // one decode mode per launch: a window starting at exponent zero anywhere selects the slow forms
