@@ -1,6 +1,6 @@
 // Batched decode + GEMM entry points and their dispatcher.
 //
-//   2 <= B <= 16 : the streaming mma.sync kernel (gemm_stream.cu) on tensors of 48 row tiles or more, HBM-bound
+//   2 <= B <= 16 : the streaming mma.sync kernel (gemm_stream.cu) on large tensors (its thresholds are in gemm_stream_try), HBM-bound
 //                  (up to B = 32 when a tuning knob asks for it);
 //   B <= 16      : else the MMA GEMV family (gemv.cu);
 //   B  > 16      : the tcgen05 / TMEM kernel (gemm_tc.cu) when the shape qualifies,
